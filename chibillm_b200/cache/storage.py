@@ -37,12 +37,14 @@ class FixedStateView:
 @dataclass(frozen=True)
 class CachePlan:
     groups: Tuple[GroupLayout, ...]
-    # per run step: ("paged", group, entry, writes) | ("state", need) | None
+    # per run step: ("paged", group, entry, writes) | ("state", need) | None, or, for a run step
+    # whose parts have several needs, ("several", (one of these per need, ...))
     steps: Tuple[Optional[tuple], ...]
+    tied: Tuple[str, ...] = ()      # groups whose values are their keys (no value arrays)
 
 
 def group_name(need: PagedKVNeed) -> str:
-    base = f"kv{need.num_kv_heads}x{need.head_dim}"
+    base = f"kv{need.num_kv_heads}x{need.head_dim}" if not need.tied_values else f"k{need.num_kv_heads}x{need.head_dim}"
     return base if need.window is None else f"{base}w{need.window}"
 
 
@@ -58,41 +60,58 @@ def plan_cache(needs: Sequence[object], cache_of: Sequence[Optional[int]], page_
     entries: Dict[str, int] = {}
     needs_of: Dict[str, PagedKVNeed] = {}
     steps: List[Optional[tuple]] = []
-    for i, need in enumerate(needs):
-        src = cache_of[i]
-        if src is not None:
-            if not (0 <= src < i) or steps[src] is None or steps[src][0] != "paged" or not steps[src][3]:
+    def paged_of(step):
+        """The paged member of a planned step (a step of several needs has at most one)."""
+        if step is not None and step[0] == "several":
+            found = [m for m in step[1] if m is not None and m[0] == "paged"]
+            return found[0] if found else None
+        return step
+
+    def plan_one(i, need, src):
+        if src is not None and isinstance(need, PagedKVNeed):
+            owner = paged_of(steps[src]) if 0 <= src < i else None
+            if owner is None or owner[0] != "paged" or not owner[3]:
                 raise CacheError("invalid_configuration",
                                  f"run step {i} reads the cache of step {src}, which owns no paged cache")
-            mine = need
-            theirs = needs_of[steps[src][1]]
-            if not isinstance(mine, PagedKVNeed) or (mine.num_kv_heads, mine.head_dim) != (
-                    theirs.num_kv_heads, theirs.head_dim):
+            theirs = needs_of[owner[1]]
+            if (need.num_kv_heads, need.head_dim, need.tied_values) != (
+                    theirs.num_kv_heads, theirs.head_dim, theirs.tied_values):
                 raise CacheError("invalid_configuration",
                                  f"run step {i} cannot read the cache of step {src}: shapes differ")
-            if mine.window != theirs.window:
+            if need.window != theirs.window:
                 # the owner's window decides which pages are given back; a reader that looks
                 # further back would meet pages that are gone
                 raise CacheError("invalid_configuration",
-                                 f"run step {i} (window {mine.window}) cannot read the cache of step {src} "
+                                 f"run step {i} (window {need.window}) cannot read the cache of step {src} "
                                  f"(window {theirs.window}): the windows differ")
-            steps.append(("paged", steps[src][1], steps[src][2], False))
-        elif isinstance(need, PagedKVNeed):
+            return ("paged", owner[1], owner[2], False)
+        if isinstance(need, PagedKVNeed):
             name = group_name(need)
             needs_of[name] = need
             entry = entries.get(name, 0)
             entries[name] = entry + 1
-            steps.append(("paged", name, entry, True))
-        elif isinstance(need, FixedStateNeed):
-            steps.append(("state", need))
-        elif need is None:
-            steps.append(None)
-        else:
-            raise CacheError("invalid_configuration", f"run step {i}: unknown cache need {need!r}")
+            return ("paged", name, entry, True)
+        if isinstance(need, FixedStateNeed):
+            return ("state", need)
+        if need is None:
+            return None
+        raise CacheError("invalid_configuration", f"run step {i}: unknown cache need {need!r}")
+
+    for i, need in enumerate(needs):
+        src = cache_of[i]
+        if isinstance(need, (tuple, list)):
+            if sum(isinstance(n, PagedKVNeed) for n in need) > 1:
+                raise CacheError("invalid_configuration", f"run step {i} asks for more than one paged cache")
+            steps.append(("several", tuple(plan_one(i, n, src) for n in need)))
+            continue
+        if src is not None and not isinstance(need, PagedKVNeed):
+            raise CacheError("invalid_configuration",
+                             f"run step {i} reads the cache of step {src} but has no paged cache need")
+        steps.append(plan_one(i, need, src))
     max_blocks = (max(max_positions, 1) + page_size - 1) // page_size if max_positions else num_pages
     groups = tuple(GroupLayout(name, n.num_kv_heads, n.head_dim, n.window, page_size, num_pages,
                                entries[name], max_blocks) for name, n in needs_of.items())
-    return CachePlan(groups, tuple(steps))
+    return CachePlan(groups, tuple(steps), tuple(name for name, n in needs_of.items() if n.tied_values))
 
 
 class CacheStorage:
@@ -105,7 +124,9 @@ class CacheStorage:
         for g in plan.groups:
             shape = (g.num_entries, g.num_pages, g.num_kv_heads, g.page_size, g.head_dim)
             self.keys[g.name] = torch.zeros(shape, dtype=runtime.dtype, device=runtime.device)
-            self.values[g.name] = torch.zeros(shape, dtype=runtime.dtype, device=runtime.device)
+            # a group whose values are its keys holds one array; readers get it under both names
+            self.values[g.name] = self.keys[g.name] if g.name in plan.tied else \
+                torch.zeros(shape, dtype=runtime.dtype, device=runtime.device)
         # the block tables' mirror on the device: row = a request's state slot
         self.tables: Dict[str, torch.Tensor] = {
             g.name: torch.full((num_slots, max(g.max_blocks, 1)), -1, dtype=torch.int32, device=runtime.device)
@@ -113,20 +134,35 @@ class CacheStorage:
         self.views: List[object] = []
         self._state_arrays: List[torch.Tensor] = []
         page_sizes = {g.name: g.page_size for g in plan.groups}
-        for step in plan.steps:
+
+        def view_of(step):
             if step is None:
-                self.views.append(None)
-            elif step[0] == "paged":
+                return None
+            if step[0] == "several":
+                return tuple(view_of(member) for member in step[1])
+            if step[0] == "paged":
                 _, name, entry, writes = step
-                self.views.append(PagedKVView(name, self.keys[name][entry], self.values[name][entry],
-                                              page_sizes[name], writes))
-            else:
-                arrays = {}
-                for aname, shape, dtype in step[1].arrays:
-                    t = torch.zeros((num_slots,) + tuple(shape), dtype=dtype, device=runtime.device)
-                    arrays[aname] = t
-                    self._state_arrays.append(t)
-                self.views.append(FixedStateView(arrays))
+                return PagedKVView(name, self.keys[name][entry], self.values[name][entry],
+                                   page_sizes[name], writes)
+            arrays = {}
+            for aname, shape, dtype in step[1].arrays:
+                dtype = runtime.dtype if dtype is None else dtype       # None: the activations' type
+                t = torch.zeros((num_slots,) + tuple(shape), dtype=dtype, device=runtime.device)
+                arrays[aname] = t
+                self._state_arrays.append(t)
+            return FixedStateView(arrays)
+
+        for step in plan.steps:
+            self.views.append(view_of(step))
+
+    def state_views(self) -> List["FixedStateView"]:
+        """Every fixed-size state view, those inside a run step of several needs included."""
+        out = []
+        for v in self.views:
+            for member in (v if isinstance(v, tuple) else (v,)):
+                if isinstance(member, FixedStateView):
+                    out.append(member)
+        return out
 
     def zero_state_slot(self, slot: int) -> None:
         for t in self._state_arrays:
@@ -135,11 +171,12 @@ class CacheStorage:
     def poison(self, value: float = float("nan")) -> None:
         """Fill every page with a marker (tests use NaN so that a read of a
         position that was never written shows)."""
-        for t in list(self.keys.values()) + list(self.values.values()):
+        for t in list(self.keys.values()) + [v for n, v in self.values.items() if n not in self.plan.tied]:
             t.fill_(value)
 
     def bytes(self) -> int:
         total = 0
-        for t in list(self.keys.values()) + list(self.values.values()) + self._state_arrays:
+        values = [v for n, v in self.values.items() if n not in self.plan.tied]
+        for t in list(self.keys.values()) + values + self._state_arrays:
             total += t.numel() * t.element_size()
         return total

@@ -20,6 +20,9 @@ class Architecture:
     model_type: Optional[str]
     read_config: Callable[[dict], Any]        # config.json object -> typed configuration
     model_spec: Callable[[Any], ModelSpec]    # typed configuration -> parts
+    # a key under which ``load_config`` adds the shapes of the folder's tensors (name -> sizes) to
+    # the object it hands to ``read_config``, for a design whose file leaves a size to the tensors
+    shapes_key: Optional[str] = None
 
 
 _BY_NAME: Dict[str, Architecture] = {}
@@ -28,10 +31,11 @@ _BY_MODEL_TYPE: Dict[str, Architecture] = {}
 
 def register_architecture(name: str, read_config: Callable[[dict], Any],
                           model_spec: Callable[[Any], ModelSpec],
-                          model_type: Optional[str] = None, replace: bool = False) -> Architecture:
+                          model_type: Optional[str] = None, replace: bool = False,
+                          shapes_key: Optional[str] = None) -> Architecture:
     if name in _BY_NAME and not replace:
         raise ValueError(f"architecture '{name}' is already registered")
-    arch = Architecture(name, model_type, read_config, model_spec)
+    arch = Architecture(name, model_type, read_config, model_spec, shapes_key)
     _BY_NAME[name] = arch
     if model_type is not None:
         _BY_MODEL_TYPE[model_type] = arch
@@ -49,8 +53,11 @@ def registered_architectures() -> list:
 
 
 def find_architecture(config_object: dict) -> Architecture:
-    """Pick the architecture that a parsed config.json names."""
+    """Pick the architecture that a parsed config.json names: the first entry of
+    "architectures", else the string "architecture", else "model_type"."""
     names = config_object.get("architectures")
+    if names is None and isinstance(config_object.get("architecture"), str):
+        names = [config_object["architecture"]]
     if isinstance(names, list) and names and isinstance(names[0], str):
         if names[0] in _BY_NAME:
             return _BY_NAME[names[0]]
@@ -69,5 +76,13 @@ def load_config(model_dir: str):
     """Read ``model_dir/config.json``; returns (architecture, typed config, spec)."""
     obj = read_config_json(model_dir)
     arch = find_architecture(obj)
+    if arch.shapes_key is not None:
+        from ..weights.safetensors_io import Checkpoint, SafetensorsError
+        try:
+            checkpoint = Checkpoint.open_model(model_dir)
+            obj = dict(obj)
+            obj[arch.shapes_key] = {n: tuple(checkpoint.info(n).shape) for n in checkpoint.names()}
+        except SafetensorsError:
+            pass                                   # the weight loader reports a missing or broken file
     config = arch.read_config(obj)
     return arch, config, arch.model_spec(config)

@@ -57,7 +57,12 @@ class AttentionSpec(MixerSpec):
 
     ``window`` None means every earlier key is visible; an integer W means the
     W most recent keys, the query's own included.  ``scale`` multiplies the
-    scores after the dot product.
+    scores after the dot product.  ``softcap`` c (None: off) then replaces a
+    score s by c * tanh(s / c).  ``distance_bias`` "log" then takes
+    r1[h] * ln(1 + r2[h] * (i - j)) off the score of query i and key j, with two
+    learned numbers per query head (tensor roles "distance_r1", "distance_r2").
+    ``tied_values``: the values are the keys as projected; there is no value
+    projection and the cache holds keys only.
     """
 
     hidden_size: int = 0
@@ -68,6 +73,45 @@ class AttentionSpec(MixerSpec):
     window: Optional[int] = None
     qk_norm: Optional[NormSpec] = None
     position: PositionSpec = PositionSpec(kind="none")
+    softcap: Optional[float] = None
+    distance_bias: Optional[str] = None
+    tied_values: bool = False
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec(MixerSpec):
+    """Linear recurrence with a state matrix per head (``head_dim`` key rows by
+    ``head_dim`` value columns, 32-bit, zero at a sequence's start).  With r, k, v
+    projections of the input, a decay per key channel
+    w = exp(-``decay_scale`` * sigmoid(W2 tanh(W1 x) + w0)) (W1 of low rank), a
+    removal rate per key channel a = sigmoid(Wa x + ba) and the unit key
+    u = k / sqrt(sum(k^2) + ``key_eps``):
+
+        S <- diag(w) S - (a * u) (u^T S) + k v^T      (both products read the old S)
+        o  = S^T r
+
+    Each head's o is divided by its root mean square (``norm_eps`` inside the
+    root), multiplied by a weight over all heads and by sigmoid(Wg x), and
+    projected back to ``hidden_size``.
+    """
+
+    hidden_size: int = 0
+    num_heads: int = 0
+    head_dim: int = 0
+    decay_rank: int = 0
+    decay_scale: float = 0.0
+    key_eps: float = 0.0
+    norm_eps: float = 0.0
+
+
+@dataclass(frozen=True)
+class ShortConvSpec:
+    """A causal convolution over time on each channel, added to its input:
+    y_t = x_t + sum_j w[:, j] * x_(t - taps + 1 + j), zeros before the sequence's
+    start.  The last ``taps`` - 1 inputs are part of a request's state."""
+
+    size: int
+    taps: int
 
 
 @dataclass(frozen=True)
@@ -87,22 +131,36 @@ class GatedMLPSpec(FeedForwardSpec):
 
 
 @dataclass(frozen=True)
+class DenseMLPSpec(FeedForwardSpec):
+    """Dense feed-forward without a gate: down(act(up(x))).  ``activation``:
+    "gelu" (exact, with erf), "gelu_tanh", "silu" or "relu"."""
+
+    hidden_size: int = 0
+    intermediate_size: int = 0
+    activation: str = "gelu"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One block: how mixer, feed-forward and norms are arranged.
 
     ``arrangement`` names a registered block ("prenorm": x + mixer(norm(x)),
     then x + ff(norm(x))).  ``weight_prefix`` is the checkpoint prefix of the
     block's tensors.  ``weight_names`` maps the part-local tensor roles to
-    checkpoint names under that prefix.
+    checkpoint names under that prefix.  ``feed_forward`` (with its norm) may be
+    None: the block then ends after the mixer.  ``mixer_conv``: a short
+    convolution between the mixer's norm and the mixer (tensor role
+    "mixer_conv").
     """
 
     arrangement: str
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: Optional[FeedForwardSpec]
     mixer_norm: NormSpec
-    feed_forward_norm: NormSpec
+    feed_forward_norm: Optional[NormSpec]
     weight_prefix: str
     weight_names: Tuple[Tuple[str, str], ...] = ()
+    mixer_conv: Optional[ShortConvSpec] = None
 
     def names(self) -> dict:
         return dict(self.weight_names)
@@ -115,10 +173,16 @@ class RunStep:
     ``layer`` indexes ``ModelSpec.layers`` (a layer may be named twice: its
     weights are shared, every run has a cache of its own).  ``cache_of`` names
     an earlier run step whose cache this step reads instead of writing one.
+    ``enter`` indexes ``ModelSpec.stream_adapters``: that adapter transforms the
+    residual stream right before this step, with ``turn`` as its argument (the
+    number of the pass that begins here, for a group of layers that runs
+    several times).
     """
 
     layer: int
     cache_of: Optional[int] = None
+    enter: Optional[int] = None
+    turn: int = 0
 
 
 @dataclass(frozen=True)
@@ -148,7 +212,7 @@ class ModelSpec:
     architecture: str
     vocab_size: int
     hidden_size: int
-    max_positions: int
+    max_positions: int                                # 0: no limit of the model's own (the cache pool bounds a request)
     layers: Tuple[LayerSpec, ...]
     run_order: Tuple[RunStep, ...]
     final_norm: NormSpec
@@ -161,3 +225,4 @@ class ModelSpec:
     extra: dict = field(default_factory=dict, compare=False)
     input_adapters: Tuple[AdapterSpec, ...] = ()      # run on the residual right after the embedding
     logit_adapters: Tuple[AdapterSpec, ...] = ()      # run on the 32-bit logits of the wanted rows
+    stream_adapters: Tuple[AdapterSpec, ...] = ()     # run on the residual where a run step's ``enter`` names them

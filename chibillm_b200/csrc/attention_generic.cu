@@ -12,6 +12,9 @@
 //
 // Query token i of sequence s sits at position ctx_len[s] - q_len[s] + i and
 // sees keys max(0, pos - window + 1) .. pos (window 0 = all).
+//
+// Options of the score: a soft cap c (0 = off) replaces s by c * tanh(s / c); a bias by
+// distance (r1, r2 per query head, null = off) then takes r1 * ln(1 + r2 * (pos - key)) off.
 #define CHIBI_UNIT attention_generic
 #define CHIBI_UNIT_ID 4
 #include "common.cuh"
@@ -29,7 +32,8 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cach
                          const int* __restrict__ seq_of_token, const int* __restrict__ seq_rows,
                          const int* __restrict__ positions,
                          long long tokens, int nq, int nkv, int d, int page_size, int num_pages,
-                         float scale, int window, int* __restrict__ error)
+                         float scale, int window, float softcap, const float* __restrict__ bias_r1,
+                         const float* __restrict__ bias_r2, int* __restrict__ error)
 {
     pdl_enter();
     extern __shared__ float smem[];
@@ -49,6 +53,7 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cach
     __syncwarp();
 
     const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const float r1 = bias_r1 ? bias_r1[head] : 0.f, r2 = bias_r1 ? bias_r2[head] : 0.f;
     const int* table = block_table + (size_t)(seq_rows ? seq_rows[seq] : seq) * table_stride;
     constexpr int SLOTS = MAX_D / 32;
     float acc[SLOTS];
@@ -73,6 +78,10 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cach
                 for (int j = 0; j < d; ++j)
                     dot = fmaf(qs[j], to_f32(krow[j]), dot);
                 s = dot * scale;
+                if (softcap > 0.f)
+                    s = softcap * tanhf(s / softcap);
+                if (bias_r1)
+                    s -= r1 * log1pf(r2 * (float)(pos - u));
             }
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -120,12 +129,13 @@ CHIBI_API int chibi_attention_generic(const void* q, int q_type, const void* k_c
                                       const int* seq_of_token, const int* seq_rows,
                                       const int* positions,
                                       long long tokens, int nq, int nkv, int d, int page_size,
-                                      int num_pages, float scale, int window, int* error,
+                                      int num_pages, float scale, int window, float softcap,
+                                      const float* bias_r1, const float* bias_r2, int* error,
                                       cudaStream_t stream)
 {
     if (tokens <= 0)
         return CHIBI_OK;
-    if (d <= 0 || d > MAX_D || nkv <= 0 || nq % nkv != 0 || window < 0)
+    if (d <= 0 || d > MAX_D || nkv <= 0 || nq % nkv != 0 || window < 0 || softcap < 0.f || (bias_r1 != nullptr) != (bias_r2 != nullptr))
         return CHIBI_ERR_UNSUPPORTED;
     const int warps = 4;
     const long long jobs = tokens * nq;
@@ -137,7 +147,7 @@ CHIBI_API int chibi_attention_generic(const void* q, int q_type, const void* k_c
         launch(attention_generic_kernel<TQ, TC>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream, 
             (const TQ*)q, (const TC*)k_cache, (const TC*)v_cache, (TQ*)out, block_table,
             table_stride, q_start, ctx_len, seq_of_token, seq_rows, positions, tokens, nq, nkv, d, page_size,
-            num_pages, scale, window, error);
+            num_pages, scale, window, softcap, bias_r1, bias_r2, error);
     }));
     return launch_status();
 }

@@ -16,6 +16,10 @@
 // Scores are (q . k) * scale in 32-bit; softmax state (running max and sum) and
 // the output accumulator are 32-bit; probabilities are rounded to bfloat16 for
 // the second product.  A row sees keys max(0, pos - window + 1) .. pos.
+//
+// Options of the score (all off for a plain model): a soft cap c replaces a scaled score s
+// by c * tanh(s / c); a bias by distance then takes r1 * ln(1 + r2 * (pos - key)) off, with
+// r1 and r2 per query head; with tied values the value tile is the key tile (one copy).
 #define CHIBI_UNIT attention_mma
 #define CHIBI_UNIT_ID 6
 #include "common.cuh"
@@ -65,6 +69,11 @@ struct AttnParams {
     float norm_eps, norm_offset;
     int append;                    // write the new key and value (0: the layer reads another layer's cache)
     int skip_single;               // prefill: leave one-token sequences to the decode kernel
+    float scale;                   // the plain scale, for the scores with options
+    float softcap;                 // 0: none
+    const float* bias_r1;          // [nq] or null
+    const float* bias_r2;
+    int tied;                      // the values are the keys: one tile serves both
     int* error;
 };
 
@@ -123,7 +132,8 @@ __device__ __forceinline__ int lookup_tile_page(const int* table, int page_size,
 __device__ __forceinline__ void load_kv_tile16_paged(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst,
                                                      const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache,
                                                      int page, int kv_head, int nkv, int page_size, int num_pages,
-                                                     int key0, int key_end, int lane, int* error)
+                                                     int key0, int key_end, int lane, int* error,
+                                                     bool tied = false)
 {
     long long off = -1;
     {
@@ -145,17 +155,19 @@ __device__ __forceinline__ void load_kv_tile16_paged(__nv_bfloat16* k_dst, __nv_
         const bool valid = o >= 0;
         const long long src = valid ? o + col * 8 : 0;
         cp_async16(k_dst + row * DPAD + col * 8, k_cache + src, valid);
-        cp_async16(v_dst + row * DPAD + col * 8, v_cache + src, valid);
+        if (!tied)
+            cp_async16(v_dst + row * DPAD + col * 8, v_cache + src, valid);
     }
 }
 
 __device__ __forceinline__ void load_kv_tile16(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst,
                                                const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache,
                                                const int* table, int kv_head, int nkv, int page_size,
-                                               int num_pages, int key0, int key_end, int lane, int* error)
+                                               int num_pages, int key0, int key_end, int lane, int* error,
+                                               bool tied = false)
 {
     load_kv_tile16_paged(k_dst, v_dst, k_cache, v_cache, lookup_tile_page(table, page_size, key0, key_end, lane),
-                         kv_head, nkv, page_size, num_pages, key0, key_end, lane, error);
+                         kv_head, nkv, page_size, num_pages, key0, key_end, lane, error, tied);
 }
 
 // Loads the A fragments of a 16-row query tile from shared memory.
@@ -217,13 +229,54 @@ __device__ __forceinline__ void pv_product(float (&o)[NTILES_D][4], const float 
 // return s holds exp2(score * scale_log2 - m_new) (0 where masked), m/l are
 // updated and o is rescaled.  `pos_lo/hi`: positions of this thread's two rows;
 // a key is visible when first_lo/hi <= key <= pos_lo/hi and key < key_end.
+// `opt` (on: some option of the score is in use): the cap and this thread's two rows' bias numbers.
+struct ScoreOptions {
+    bool on;
+    float scale, cap, inv_cap;
+    float r1[2], r2[2];                 // of the thread's low and high row
+};
+
+__device__ __forceinline__ ScoreOptions score_options(const AttnParams& p, int head_lo, int head_hi)
+{
+    ScoreOptions o;
+    o.on = p.softcap > 0.f || p.bias_r1 != nullptr;
+    o.scale = p.scale;
+    o.cap = p.softcap;
+    o.inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+    const bool b = p.bias_r1 != nullptr;
+    o.r1[0] = b && head_lo >= 0 ? p.bias_r1[head_lo] : 0.f;
+    o.r2[0] = b && head_lo >= 0 ? p.bias_r2[head_lo] : 0.f;
+    o.r1[1] = b && head_hi >= 0 ? p.bias_r1[head_hi] : 0.f;
+    o.r2[1] = b && head_hi >= 0 ? p.bias_r2[head_hi] : 0.f;
+    return o;
+}
+
 template <int NT>
 __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[NTILES_D][4], float (&m)[2],
                                              float (&l)[2], float scale_log2, int key0, int key_end,
-                                             int pos_lo, int pos_hi, int first_lo, int first_hi, int lane)
+                                             int pos_lo, int pos_hi, int first_lo, int first_hi, int lane,
+                                             const ScoreOptions& opt)
 {
     const int tig = lane & 3;
     float mx[2] = { -INFINITY, -INFINITY };
+    if (opt.on) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key0 + nt * 8 + tig * 2 + (e & 1);
+                const int hi = e >> 1;
+                const int pos = hi ? pos_hi : pos_lo;
+                const bool vis = key < key_end && key <= pos && key >= (hi ? first_hi : first_lo);
+                float v = s[nt][e] * opt.scale;
+                if (opt.cap > 0.f)
+                    v = opt.cap * tanhf(v * opt.inv_cap);
+                v -= opt.r1[hi] * log1pf(opt.r2[hi] * (float)max(pos - key, 0));
+                s[nt][e] = vis ? v * 1.4426950408889634f : -INFINITY;
+                mx[hi] = fmaxf(mx[hi], s[nt][e]);
+            }
+        }
+    } else {
     // a tile that every row of the warp sees whole needs no masks (most tiles of a long prompt)
     const int last_key = key0 + NT * 8 - 1;
     const bool whole = __all_sync(0xffffffffu, last_key < key_end && last_key <= pos_lo && last_key <= pos_hi
@@ -248,6 +301,7 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[NTILE
             s[nt][e] = vis ? s[nt][e] * scale_log2 : -INFINITY;
             mx[hi] = fmaxf(mx[hi], s[nt][e]);
         }
+    }
     }
     float corr[2], base[2];
 #pragma unroll
@@ -402,6 +456,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     const int* table = p.block_table + (size_t)(p.seq_rows ? p.seq_rows[seq] : seq) * p.table_stride;
     const int rows = min(16, p.group - row_block * 16);          // query heads in this tile
     const int head0 = kv_head * p.group + row_block * 16;
+    const ScoreOptions opt = score_options(p, (lane >> 2) < rows ? head0 + (lane >> 2) : -1,
+                                           (lane >> 2) + 8 < rows ? head0 + (lane >> 2) + 8 : -1);
 
     __nv_bfloat16* my_pipe = pipe + (size_t)warp * DEC_STAGES * DEC_STAGE_ELEMS;
     const int my_first_tile = tile_begin + warp;
@@ -435,7 +491,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
                 page_ahead = lookup_tile_page(table, p.page_size, key0_of(i + 1), key_end, lane);
             __nv_bfloat16* st = my_pipe + (size_t)(i % DEC_STAGES) * DEC_STAGE_ELEMS;
             load_kv_tile16_paged(st, st + DEC_TILE * DPAD, p.k_cache, p.v_cache, page, kv_head, p.nkv,
-                                 p.page_size, p.num_pages, key0_of(i), key_end, lane, p.error);
+                                 p.page_size, p.num_pages, key0_of(i), key_end, lane, p.error, p.tied != 0);
         }
         cp_async_commit();
     };
@@ -504,11 +560,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
         cp_async_wait<DEC_STAGES - 1>();
         __syncwarp();
         const __nv_bfloat16* k_tile = my_pipe + (size_t)(i % DEC_STAGES) * DEC_STAGE_ELEMS;
-        const __nv_bfloat16* v_tile = k_tile + DEC_TILE * DPAD;
+        const __nv_bfloat16* v_tile = p.tied ? k_tile : k_tile + DEC_TILE * DPAD;
         const int key0 = first + (my_first_tile + i * DEC_WARPS) * DEC_TILE;
         float s[2][4] = { { 0.f, 0.f, 0.f, 0.f }, { 0.f, 0.f, 0.f, 0.f } };
         qk_product<2>(s, qf, q_tile, k_tile, lane);
-        softmax_tile<2>(s, o, m, l, p.scale_log2, key0, key_end, pos, pos, first, first, lane);
+        softmax_tile<2>(s, o, m, l, p.scale_log2, key0, key_end, pos, pos, first, first, lane, opt);
         pv_product<2>(o, s, v_tile, lane);
         __syncwarp();
     }
@@ -663,6 +719,8 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, PRE_Q_ALIASED ? 3 : 1) attn_pr
     const int pos_hi = r_hi < rows_total ? pos0 + r_hi / p.group : -1;
     const int first_lo = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
     const int first_hi = (p.window > 0 && pos_hi - p.window + 1 > 0) ? pos_hi - p.window + 1 : 0;
+    const ScoreOptions opt = score_options(p, r_lo < rows_total ? kv_head * p.group + r_lo % p.group : -1,
+                                           r_hi < rows_total ? kv_head * p.group + r_hi % p.group : -1);
     // rows of this warp: positions between warp_min_pos and warp_max_pos
     const int w_first_row = row0 + warp * 16;
     const int w_last_row = min(rows_total, w_first_row + 16) - 1;
@@ -679,7 +737,7 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, PRE_Q_ALIASED ? 3 : 1) attn_pr
             for (int sub = warp; sub < PRE_KEYS / 16; sub += PRE_WARPS)
                 load_kv_tile16(st + sub * 16 * DPAD, st + (PRE_KEYS + sub * 16) * DPAD, p.k_cache, p.v_cache,
                                table, kv_head, p.nkv, p.page_size, p.num_pages, key0 + sub * 16, key_end,
-                               lane, p.error);
+                               lane, p.error, p.tied != 0);
         }
         cp_async_commit();
     };
@@ -703,7 +761,7 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, PRE_Q_ALIASED ? 3 : 1) attn_pr
         cp_async_wait<1>();
         __syncthreads();
         const __nv_bfloat16* k_tile = kv + (size_t)(i & 1) * 2 * PRE_KEYS * DPAD;
-        const __nv_bfloat16* v_tile = k_tile + PRE_KEYS * DPAD;
+        const __nv_bfloat16* v_tile = p.tied ? k_tile : k_tile + PRE_KEYS * DPAD;
         const int key0 = key_begin + i * PRE_KEYS;
         // skip tiles that no row of this warp can see
         if (warp_active && key0 <= warp_max_pos && key0 + PRE_KEYS > warp_min_first) {
@@ -712,7 +770,7 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, PRE_Q_ALIASED ? 3 : 1) attn_pr
             for (int nt = 0; nt < PRE_NT; ++nt)
                 s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
             qk_product<PRE_NT>(s, qf, my_q, k_tile, lane);
-            softmax_tile<PRE_NT>(s, o, m, l, p.scale_log2, key0, key_end, pos_lo, pos_hi, first_lo, first_hi, lane);
+            softmax_tile<PRE_NT>(s, o, m, l, p.scale_log2, key0, key_end, pos_lo, pos_hi, first_lo, first_hi, lane, opt);
             pv_product<PRE_NT>(o, s, v_tile, lane);
         }
         __syncthreads();                   // the stage may be overwritten by the next issue
@@ -754,12 +812,13 @@ CHIBI_API int chibi_attention_mma(const void* q, const void* k_cache, const void
                                   const int* block_table, int table_stride, const int* seq_rows,
                                   const int* q_start, const int* ctx_len, int seqs, int nq, int nkv, int page_size,
                                   int num_pages, float scale, int window, int mode, int max_q_len,
-                                  int splits, float* scratch, long long scratch_floats, int* error,
-                                  cudaStream_t stream)
+                                  int splits, float* scratch, long long scratch_floats, float softcap,
+                                  const float* bias_r1, const float* bias_r2, int* error, cudaStream_t stream)
 {
     if (seqs <= 0)
         return CHIBI_OK;
-    if (nkv <= 0 || nq % nkv != 0 || window < 0 || page_size <= 0 || splits < 1)
+    if (nkv <= 0 || nq % nkv != 0 || window < 0 || page_size <= 0 || splits < 1 || softcap < 0.f
+        || (bias_r1 != nullptr) != (bias_r2 != nullptr))
         return CHIBI_ERR_ARGUMENT;
     AttnParams p {};
     p.q = static_cast<const __nv_bfloat16*>(q);
@@ -781,6 +840,11 @@ CHIBI_API int chibi_attention_mma(const void* q, const void* k_cache, const void
     p.splits = splits;
     p.error = error;
     p.skip_single = (mode & 1) ? 1 : 0;
+    p.scale = scale;
+    p.softcap = softcap;
+    p.bias_r1 = bias_r1;
+    p.bias_r2 = bias_r2;
+    p.tied = k_cache == v_cache ? 1 : 0;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM);

@@ -102,6 +102,13 @@ rmsnorm_f32_bf16_kernel(const float* x, const __nv_bfloat16* __restrict__ w, __n
     }
 }
 
+// `append`: 0 = query heads only (the layer reads another layer's cache), 1 = keys and values
+// are appended, 2 = keys only (a layer whose values are its keys: q | k has no value columns).
+__host__ __device__ __forceinline__ int head_jobs(int nq, int nkv, int append)
+{
+    return append == 1 ? nq + 2 * nkv : (append == 2 ? nq + nkv : nq);
+}
+
 // ------------------------------------------- per-head norm + rotation + append
 // grid (tokens, ceil(jobs / warps)), one warp per head job.  Jobs 0..nq-1 are
 // query heads, nq..nq+nkv-1 key heads, the rest value heads.  Query and key
@@ -138,7 +145,7 @@ __global__ void qk_norm_rope_append_kernel(
         cs[half + j] = sn;
     }
     __syncthreads();
-    const int jobs = append ? nq + 2 * nkv : nq;
+    const int jobs = head_jobs(nq, nkv, append);
     const int job = blockIdx.y * warps + warp;
     if (job >= jobs)
         return;
@@ -313,7 +320,7 @@ __global__ void qk_norm_rope_append_vec4_kernel(
     // kernel: the token's cache slot and its cosines and sines are worked out while the
     // kernel before this one still runs.
     const int pos = positions[t];
-    const int jobs = append ? nq + 2 * nkv : nq;
+    const int jobs = head_jobs(nq, nkv, append);
     const int job0 = (blockIdx.y * warps + warp) * JPW;
     long long cache_base = -1;                // the token's slot in the caches, head 0
     if (append && job0 + JPW > nq) {
@@ -441,7 +448,7 @@ __global__ void __launch_bounds__(ROWS_KERNEL_WARPS * 32) qk_norm_rope_append_d1
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pos = positions[t];
-    const int jobs = append ? nq + 2 * nkv : nq;
+    const int jobs = head_jobs(nq, nkv, append);
     long long cache_base = -1;
     if (append) {
         const int seq = seq_of_token[t];
@@ -698,7 +705,7 @@ CHIBI_API int chibi_qk_norm_rope_append(
         return CHIBI_OK;
     if (d <= 0 || d > 256 || rot < 0 || rot > d || (rot & 1))
         return CHIBI_ERR_UNSUPPORTED;
-    const int jobs = append ? nq + 2 * nkv : nq;
+    const int jobs = head_jobs(nq, nkv, append);
     const int warps = jobs < 8 ? jobs : 8;
     const size_t smem = (size_t)(warps * d + rot) * sizeof(float);
     const dim3 grid((unsigned)tokens, (unsigned)((jobs + warps - 1) / warps));
@@ -706,8 +713,8 @@ CHIBI_API int chibi_qk_norm_rope_append(
         return CHIBI_ERR_UNSUPPORTED;
     const bool aligned = d % 4 == 0 && qkv_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0
         && (reinterpret_cast<uintptr_t>(q_out) & 15) == 0 && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0
-        && (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0;
-    if (aligned && d == 128 && rot == d && tokens >= 32 && jobs <= ROWS_KERNEL_WARPS * ROWS_KERNEL_MAX_JOBS) {
+        && (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0 && (rot == 0 || inv_freq != nullptr);
+    if (aligned && append != 2 && d == 128 && rot == d && tokens >= 32 && jobs <= ROWS_KERNEL_WARPS * ROWS_KERNEL_MAX_JOBS) {
         CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(w_type, TW, CHIBI_DISPATCH_TYPE(cache_type, TC, {
             launch(qk_norm_rope_append_d128_kernel<TX, TW, TC>, dim3((unsigned)tokens),
                    dim3(ROWS_KERNEL_WARPS * 32), 0, stream, (const TX*)qkv, qkv_stride, (TX*)q_out, (TC*)k_cache,
@@ -754,7 +761,7 @@ CHIBI_API int chibi_qk_norm_rope_append_partial(
     if (d <= 0 || d > 256 || d % 4 != 0 || rot < 0 || rot > d || (rot & 1) || width % 4 != 0
         || splits < 1 || (reinterpret_cast<uintptr_t>(partial) & 15))
         return CHIBI_ERR_UNSUPPORTED;
-    const int jobs = append ? nq + 2 * nkv : nq;
+    const int jobs = head_jobs(nq, nkv, append);
     const int warps = jobs < 8 ? jobs : 8;
     const int per_block = warps;
     const size_t smem = (size_t)(per_block * d + rot) * sizeof(float);

@@ -27,11 +27,16 @@ class DecoderModel:
         self.final_norm = make_norm(spec.final_norm, spec.final_norm_name, runtime)
         self.input_adapters = [make_adapter(a, runtime) for a in spec.input_adapters]
         self.logit_adapters = [make_adapter(a, runtime) for a in spec.logit_adapters]
+        self.stream_adapters = [make_adapter(a, runtime) for a in spec.stream_adapters]
         self.embedding: torch.Tensor = None
         self.output: torch.Tensor = None
         for i, step in enumerate(spec.run_order):
             if not (0 <= step.layer < len(self.blocks)):
                 raise ValueError(f"run step {i} names layer {step.layer}; the model has {len(self.blocks)}")
+            if step.enter is not None and not (0 <= step.enter < len(self.stream_adapters)):
+                raise ValueError(f"run step {i} names stream adapter {step.enter}; the model has "
+                                 f"{len(self.stream_adapters)}")
+        self._keep_embedding_output = any(a.needs_embedding_output for a in self.stream_adapters)
 
     # ---- weights
     def expected_tensors(self, available: Optional[Iterable[str]] = None) -> List[TensorSpec]:
@@ -45,7 +50,7 @@ class DecoderModel:
             out.append(TensorSpec(s.output_name, (s.vocab_size, s.hidden_size)))
         for b in self.blocks:
             out += b.expected_tensors()
-        for a in self.input_adapters + self.logit_adapters:
+        for a in self.input_adapters + self.logit_adapters + self.stream_adapters:
             out += a.expected_tensors()
         return out
 
@@ -56,12 +61,12 @@ class DecoderModel:
         self.final_norm.bind(tensors)
         for b in self.blocks:
             b.bind(tensors)
-        for a in self.input_adapters + self.logit_adapters:
+        for a in self.input_adapters + self.logit_adapters + self.stream_adapters:
             a.bind(tensors)
 
     # ---- cache
     def cache_needs(self) -> List[object]:
-        return [self.blocks[step.layer].mixer.cache_need() for step in self.spec.run_order]
+        return [self.blocks[step.layer].cache_need() for step in self.spec.run_order]
 
     def cache_sources(self) -> List[Optional[int]]:
         return [step.cache_of for step in self.spec.run_order]
@@ -71,7 +76,7 @@ class DecoderModel:
         numbers of tokens, sequences and wanted rows), as a hashable; None if any
         part cannot promise that a captured step stays valid."""
         keys = []
-        for a in self.input_adapters + self.logit_adapters:
+        for a in self.input_adapters + self.logit_adapters + self.stream_adapters:
             key = a.launch_key(ctx)
             if key is None:
                 return None
@@ -96,8 +101,17 @@ class DecoderModel:
         k.embed(ctx.tokens, self.embedding, residual)
         for a in self.input_adapters:
             a.forward(residual, ctx)
+        if self._keep_embedding_output:
+            kept = ctx.workspace.get("model.embedding_output", (T, hidden), torch.float32)
+            k.cast(residual, kept)
+            ctx.shared["embedding output"] = kept
         pending = None      # a last product that a block left to be added to the residual
         for i, step in enumerate(self.spec.run_order):
+            if step.enter is not None:
+                if pending is not None:
+                    pending.add_into(residual)
+                    pending = None
+                self.stream_adapters[step.enter].forward(residual, ctx, step.turn)
             pending = self.blocks[step.layer].forward(residual, ctx, cache_views[i], pending)
         if pending is not None:
             pending.add_into(residual)

@@ -50,7 +50,7 @@ def make_runtime(dtype, device="cuda:0", kernels=None, spec=None) -> Runtime:
         from ..kernels.ops import CudaKernels
         if spec is not None:
             from ..csrc import build
-            head_dims = {getattr(layer.mixer, "head_dim", 0) for layer in spec.layers}
+            head_dims = {layer.mixer.head_dim for layer in spec.layers if layer.mixer.kind == "attention"}
             build.prepare(head_dims, bfloat16=parse_dtype(dtype) == torch.bfloat16)
         kernels = CudaKernels(device)
     return Runtime(device=device, dtype=parse_dtype(dtype), kernels=kernels)
@@ -67,6 +67,8 @@ class ModelRunner:
         self.spec = model.spec
         self.runtime = runtime
         self.page_size = page_size
+        # a model without a limit of its own: the pool bounds a request
+        self.max_positions = model.spec.max_positions or (1 << 30)
         plan = plan_cache(model.cache_needs(), model.cache_sources(), page_size, pool_tokens,
                           model.spec.max_positions)
         self.plan = plan
@@ -88,7 +90,7 @@ class ModelRunner:
         self._ahead: Optional[dict] = None
         self.steps_ahead_used = 0
         self.steps_ahead_dropped = 0
-        self._has_state = any(isinstance(v, FixedStateView) for v in self.storage.views)
+        self._has_state = bool(self.storage.state_views())
         # the last step, if it was run with ``provisional=True`` and is neither settled nor rolled
         # back yet: (request ids, lengths before, saved rows of the fixed-size state)
         self._provisional: Optional[tuple] = None
@@ -126,8 +128,8 @@ class ModelRunner:
     def max_context_tokens(self) -> int:
         """min(model's positions, what the smallest pool holds)
         (src/qwen/qwen_model_runner.cc:128-134)."""
-        pool = min((g.num_pages * g.page_size for g in self.plan.groups), default=self.spec.max_positions)
-        return min(self.spec.max_positions, pool)
+        pool = min((g.num_pages * g.page_size for g in self.plan.groups), default=self.max_positions)
+        return min(self.max_positions, pool)
 
     # ------------------------------------------------------------ requests
     def admit(self, request_id: Hashable) -> None:
@@ -191,7 +193,7 @@ class ModelRunner:
                 self._meta_copied.synchronize()     # the pinned array may still be read by the last copy
             status = native.runtime().chibi_pack_step(
                 cache.handle, S, ids, n_tokens, tokens, n_want, want, self.spec.vocab_size,
-                self.spec.max_positions, 1 if fixed_update_capacity else 0, host.data_ptr(), host.numel(),
+                self.max_positions, 1 if fixed_update_capacity else 0, host.data_ptr(), host.numel(),
                 info, len(info))
             if status == 0:
                 break
@@ -303,7 +305,7 @@ class ModelRunner:
                 or device_tokens.dtype != torch.int32 or not device_tokens.is_cuda:
             return False
         for rid in request_ids:
-            if not self.cache.has(rid) or self.cache.length(rid) + 1 > self.spec.max_positions:
+            if not self.cache.has(rid) or self.cache.length(rid) + 1 > self.max_positions:
                 return False
         try:
             for rid in request_ids:
@@ -350,10 +352,9 @@ class ModelRunner:
         if self._has_state:
             slots = torch.tensor([self.cache.state_slot(e.request_id) for e in entries], dtype=torch.long,
                                  device=self.runtime.device)
-            for view in self.storage.views:
-                if isinstance(view, FixedStateView):
-                    for t in view.arrays.values():
-                        saved.append((t, slots, t.index_select(0, slots)))
+            for view in self.storage.state_views():
+                for t in view.arrays.values():
+                    saved.append((t, slots, t.index_select(0, slots)))
         self._provisional = ([e.request_id for e in entries], list(old_lengths), saved)
 
     def settle_step(self) -> None:

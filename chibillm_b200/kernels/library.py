@@ -45,7 +45,15 @@ _SIGNATURES = {
         "chibi_reduce_swiglu": [P, I, I, I, P, I, I, P],
         "chibi_qk_norm_rope_append_partial": [P, I, L, L, P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I,
                                               I, I, F, F, I, P, P],
-        "chibi_attention_generic": [P, I, P, P, I, P, P, I, P, P, P, P, P, L, I, I, I, I, I, F, I, P, P],
+        "chibi_attention_generic": [P, I, P, P, I, P, P, I, P, P, P, P, P, L, I, I, I, I, I, F, I, F, P, P, P, P],
+        "chibi_short_conv": [P, I, L, P, P, P, L, P, P, I, I, I, I, P],
+        "chibi_delta_rule": [P, I, L, P, P, P, P, P, P, P, I, I, I, I, I, F, F, P],
+        "chibi_gated_group_norm": [P, P, I, L, P, P, I, L, I, I, F, P],
+        "chibi_scale": [P, F, L, P],
+        "chibi_cast_rows": [P, I, L, P, I, L, L, I, P],
+        "chibi_add_row_vector": [P, L, P, L, I, P],
+        "chibi_activation": [P, I, L, I, P],
+        "chibi_reduce_activation": [P, I, L, P, I, I, P],
         "chibi_sample": [P, L, L, I, P, P, P, P, L, P],
     },
     "chibi_attention_tc": {
@@ -54,7 +62,7 @@ _SIGNATURES = {
     },
     "chibi_attention_mma": {
         "chibi_attention_mma_head_dim": [],
-        "chibi_attention_mma": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, P, L, P, P],
+        "chibi_attention_mma": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, P, L, F, P, P, P, P],
         "chibi_attention_decode_fused": [P, I, L, L, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, P, L, P, P, P,
                                          F, F, I, P, P],
     },

@@ -622,12 +622,13 @@ class CudaKernels:
                    block_table, seq_rows)
         T = pending.M
         append = k_cache is not None
-        width = (nq + 2 * nkv) * d if append else nq * d
+        tied = append and v_cache is None       # the values are the keys: q | k, keys only
+        width = (nq + (1 if tied else 2) * nkv) * d if append else nq * d
         if pending.N != width or q_out.shape != (T, nq * d) or q_out.dtype != torch.bfloat16 \
                 or not q_out.is_contiguous():
             raise KernelError("qk_norm_rope_append_partial: shapes")
         if append and (k_cache.dtype != torch.bfloat16 or tuple(k_cache.shape[1:]) != (nkv, page_size, d)
-                       or not k_cache.is_contiguous() or not v_cache.is_contiguous()):
+                       or not k_cache.is_contiguous() or not (tied or v_cache.is_contiguous())):
             raise KernelError("qk_norm_rope_append_partial: cache")
         w_type = _code(q_norm_w) if q_norm_w is not None else F32
         self.launches += 1
@@ -636,7 +637,7 @@ class CudaKernels:
             _ptr(q_norm_w), _ptr(k_norm_w), w_type, _ptr(inv_freq), _ptr(positions), _ptr(seq_of_token),
             _ptr(seq_rows), _ptr(block_table), block_table.stride(0) if append else 0, nq, nkv, d,
             int(rotary_dim), page_size, k_cache.shape[0] if append else 0, float(eps), float(norm_offset),
-            1 if append else 0, _ptr(self.error), self._stream()), "qk_norm_rope_append_partial")
+            (2 if tied else 1) if append else 0, _ptr(self.error), self._stream()), "qk_norm_rope_append_partial")
 
     def linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
                residual: Optional[torch.Tensor] = None, defer: bool = False) -> Optional[PendingSum]:
@@ -699,13 +700,15 @@ class CudaKernels:
         first ``rotary_dim`` features, then q -> q_out, k and v -> cache pages.
         qkv: [T, (nq + 2 nkv) d], or [T, nq d] when no cache is given (the layer
         then reads another layer's cache).  Cache: [pages, nkv, page_size, d].
-        Sequence s uses row ``seq_rows[s]`` of the block table (row s when None)."""
+        Sequence s uses row ``seq_rows[s]`` of the block table (row s when None).
+        A key cache without a value cache: the values are the keys, qkv is q | k."""
         _need_cuda(qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, inv_freq, positions,
                    seq_of_token, block_table, seq_rows)
         _rows_contiguous(qkv, "qk_norm_rope_append: qkv")
         T = qkv.shape[0]
         append = k_cache is not None
-        width = (nq + 2 * nkv) * d if append else nq * d
+        tied = append and v_cache is None
+        width = (nq + (1 if tied else 2) * nkv) * d if append else nq * d
         if qkv.shape[1] < width or not q_out.is_contiguous() or q_out.shape != (T, nq * d):
             raise KernelError("qk_norm_rope_append: qkv / q_out shapes")
         if q_out.dtype != qkv.dtype:
@@ -718,8 +721,8 @@ class CudaKernels:
         num_pages = 0
         table_stride = 0
         if append:
-            if (k_cache.shape != v_cache.shape or k_cache.dim() != 4 or not k_cache.is_contiguous()
-                    or not v_cache.is_contiguous() or tuple(k_cache.shape[1:]) != (nkv, page_size, d)):
+            if (k_cache.dim() != 4 or not k_cache.is_contiguous() or tuple(k_cache.shape[1:]) != (nkv, page_size, d)
+                    or not (tied or (k_cache.shape == v_cache.shape and v_cache.is_contiguous()))):
                 raise KernelError(f"qk_norm_rope_append: cache shape {tuple(k_cache.shape)}")
             num_pages = k_cache.shape[0]
             _rows_contiguous(block_table, "qk_norm_rope_append: block_table")
@@ -732,20 +735,34 @@ class CudaKernels:
             _ptr(inv_freq), _ptr(positions), _ptr(seq_of_token), _ptr(seq_rows), _ptr(block_table),
             table_stride, T,
             nq, nkv, d, int(rotary_dim), page_size, num_pages, float(eps), float(norm_offset),
-            1 if append else 0, _ptr(self.error), self._stream()), "qk_norm_rope_append")
+            (2 if tied else 1) if append else 0, _ptr(self.error), self._stream()), "qk_norm_rope_append")
 
     def attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                   out: torch.Tensor, block_table: torch.Tensor, q_start: torch.Tensor,
                   ctx_len: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor,
                   nq: int, nkv: int, d: int, page_size: int, scale: float,
                   window: Optional[int], max_q_len: int, max_ctx_len: int, min_q_len: int = 0,
-                  seq_rows: Optional[torch.Tensor] = None) -> None:
+                  seq_rows: Optional[torch.Tensor] = None, softcap: Optional[float] = None,
+                  distance_bias=None) -> None:
         """Causal attention of every token over its sequence's pages.  bfloat16
         with a head size that is a multiple of 16 runs on the tensor cores (one
         library per head size, compiled when first needed); everything else, the
-        32-bit path included, runs the plain kernel."""
+        32-bit path included, runs the plain kernel.  ``softcap`` c: a scaled score
+        s becomes c * tanh(s / c).  ``distance_bias`` (r1, r2), float32 [nq] each:
+        r1[h] * ln(1 + r2[h] * (i - j)) is taken off the score of query i and key j.
+        ``v_cache`` may be ``k_cache`` itself (values tied to the keys)."""
         _need_cuda(q, k_cache, v_cache, out, block_table, q_start, ctx_len, seq_of_token, positions,
                    seq_rows)
+        r1 = r2 = None
+        if distance_bias is not None:
+            r1, r2 = distance_bias
+            _need_cuda(r1, r2)
+            if r1.dtype != torch.float32 or r2.dtype != torch.float32 or r1.numel() != nq or r2.numel() != nq \
+                    or not r1.is_contiguous() or not r2.is_contiguous():
+                raise KernelError("attention: the distance bias is two contiguous float32 [nq] tensors")
+        cap = float(softcap) if softcap is not None else 0.0
+        if cap < 0.0:
+            raise KernelError("attention: the soft cap must be positive")
         T = q.shape[0]
         if not q.is_contiguous() or not out.is_contiguous() or q.shape != (T, nq * d) or out.shape != q.shape:
             raise KernelError("attention: q / out must be contiguous [T, nq*d]")
@@ -758,7 +775,7 @@ class CudaKernels:
         if (self.use_tensor_cores and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
                 and d % 16 == 0 and d <= 256):
             self._attention_mma(q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d,
-                                page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows)
+                                page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows, cap, r1, r2)
             return
         self.launches += 1
         _check(self.lib.chibi_attention_generic(
@@ -766,7 +783,7 @@ class CudaKernels:
             _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(ctx_len),
             _ptr(seq_of_token), _ptr(seq_rows), _ptr(positions), T, nq, nkv, d, page_size,
             k_cache.shape[0],
-            float(scale), int(window or 0), _ptr(self.error), self._stream()), "attention")
+            float(scale), int(window or 0), cap, _ptr(r1), _ptr(r2), _ptr(self.error), self._stream()), "attention")
 
     def decode_attention_splits(self, seqs: int, nq: int, nkv: int, max_ctx_len: int) -> int:
         """Key ranges per sequence of the decode attention kernel: as many CTAs as
@@ -809,7 +826,8 @@ class CudaKernels:
         return max(1, min(8, self.sm_count // ctas, max_ctx_len // 512))
 
     def _attention_mma(self, q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d,
-                       page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows) -> None:
+                       page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows,
+                       softcap: float = 0.0, bias_r1=None, bias_r2=None) -> None:
         lib = self._attention_libs.get(d)
         if lib is None:
             lib = self._load("chibi_attention_mma", (f"CHIBI_HEAD_DIM={d}",))
@@ -818,7 +836,8 @@ class CudaKernels:
             lib = self._attention_libs[d] = self._profiled(lib)
         seqs = ctx_len.numel()
         mode = 1 if max_q_len == 1 else (2 if min_q_len > 1 else 3)
-        if mode & 2 and self.use_tcgen05_attention and d in build.TCGEN05_ATTENTION_HEAD_DIMS \
+        plain_scores = softcap == 0.0 and bias_r1 is None and k_cache.data_ptr() != v_cache.data_ptr()
+        if mode & 2 and plain_scores and self.use_tcgen05_attention and d in build.TCGEN05_ATTENTION_HEAD_DIMS \
                 and page_size >= 8 and 128 % page_size == 0:
             # prompt portions on tcgen05; one-token sequences stay with the split-key kernel
             tc = self._attention_tc_libs.get(d)
@@ -852,7 +871,8 @@ class CudaKernels:
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
             _ptr(seq_rows), _ptr(q_start), _ptr(ctx_len), seqs, nq, nkv, page_size, k_cache.shape[0], float(scale),
             int(window or 0), mode, int(max_q_len), splits, _ptr(scratch),
-            scratch.numel() if scratch is not None else 0, _ptr(self.error), self._stream())
+            scratch.numel() if scratch is not None else 0, float(softcap), _ptr(bias_r1), _ptr(bias_r2),
+            _ptr(self.error), self._stream())
         self.launches += (1 if mode & 1 else 0) + (1 if mode & 1 and splits > 1 else 0) + (1 if mode & 2 else 0)
         _check(status, "attention (tensor cores)")
 
@@ -927,6 +947,128 @@ class CudaKernels:
         self.launches += 1
         _check(self.lib.chibi_swiglu(_ptr(gate_up), _code(gate_up), _ptr(out), _code(out),
                                      out.shape[0], out.shape[1], self._stream()), "swiglu")
+
+    # ---- parts with a fixed-size state, and the row-wise helpers around them
+    def short_conv(self, x: torch.Tensor, weight: torch.Tensor, history: torch.Tensor, out: torch.Tensor,
+                   q_start: torch.Tensor, positions: torch.Tensor, state_slots: torch.Tensor, max_q_len: int) -> None:
+        """out_t = x_t + sum_j weight[:, j] * x_(t - taps + 1 + j) along each sequence of
+        the step.  ``history`` [slots, max(taps - 1, 1), D] (x's type, oldest first)
+        gives what lies before a sequence's first token of the step and takes the
+        sequence's last taps - 1 inputs."""
+        _need_cuda(x, weight, history, out, q_start, state_slots)
+        _rows_contiguous(x, "short_conv: x")
+        _rows_contiguous(out, "short_conv: out")
+        T, D = x.shape
+        taps = weight.shape[1]
+        if weight.shape != (D, taps) or weight.dtype != torch.float32 or not weight.is_contiguous() \
+                or out.shape != x.shape or out.dtype != x.dtype or history.dtype != x.dtype \
+                or not history.is_contiguous() or tuple(history.shape[1:]) != (max(taps - 1, 1), D) \
+                or out.data_ptr() == x.data_ptr():
+            raise KernelError("short_conv: weight float32 [D, taps], history [slots, taps - 1, D] and out of x's type")
+        self.launches += 1
+        _check(self.lib.chibi_short_conv(_ptr(x), _code(x), x.stride(0), _ptr(weight), _ptr(history), _ptr(out),
+                                         out.stride(0), _ptr(q_start), _ptr(state_slots), state_slots.numel(),
+                                         int(max_q_len), D, taps, self._stream()), "short_conv")
+
+    def delta_rule(self, proj: torch.Tensor, decay_out: torch.Tensor, decay_bias: torch.Tensor,
+                   removal_bias: torch.Tensor, state: torch.Tensor, o: torch.Tensor, q_start: torch.Tensor,
+                   state_slots: torch.Tensor, heads: int, d: int, rank: int, decay_scale: float, key_eps: float,
+                   max_q_len: int) -> None:
+        """The generalised delta rule over the step's tokens of every sequence.
+        ``proj`` [T, 5 * heads * d + rank] holds r | k | v | gate | removal | low.  Per
+        head: w = exp(-decay_scale * sigmoid(decay_out tanh(low) + decay_bias)),
+        a = sigmoid(removal + removal_bias), u = k / sqrt(sum(k^2) + key_eps);
+        S <- diag(w) S - (a u)(u^T S) + k v^T; o = S^T r.  ``state`` [slots, heads, d, d]
+        float32 holds S with the value index before the key index."""
+        _need_cuda(proj, decay_out, decay_bias, removal_bias, state, o, q_start, state_slots)
+        _rows_contiguous(proj, "delta_rule: proj")
+        T = proj.shape[0]
+        W = heads * d
+        for t, shape, what in ((decay_out, (W, rank), "decay_out"), (decay_bias, (W,), "decay_bias"),
+                               (removal_bias, (W,), "removal_bias"), (o, (T, W), "o")):
+            if t.dtype != torch.float32 or tuple(t.shape) != shape or not t.is_contiguous():
+                raise KernelError(f"delta_rule: {what} must be contiguous float32 {shape}")
+        if proj.shape[1] != 5 * W + rank or state.dtype != torch.float32 or not state.is_contiguous() \
+                or tuple(state.shape[1:]) != (heads, d, d):
+            raise KernelError("delta_rule: proj [T, 5 * heads * d + rank] and state float32 [slots, heads, d, d]")
+        self.launches += 1
+        _check(self.lib.chibi_delta_rule(_ptr(proj), _code(proj), proj.stride(0), _ptr(decay_out), _ptr(decay_bias),
+                                         _ptr(removal_bias), _ptr(state), _ptr(o), _ptr(q_start), _ptr(state_slots),
+                                         state_slots.numel(), int(max_q_len), heads, d, rank, float(decay_scale),
+                                         float(key_eps), self._stream()), "delta_rule")
+
+    def gated_group_norm(self, x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, group: int,
+                         out: torch.Tensor) -> None:
+        """out = x / sqrt(mean(x^2 over each run of ``group`` features) + eps) * weight * sigmoid(gate)."""
+        _need_cuda(x, gate, weight, out)
+        _rows_contiguous(gate, "gated_group_norm: gate")
+        T, W = x.shape
+        if x.dtype != torch.float32 or not x.is_contiguous() or W % group != 0 or gate.shape != x.shape \
+                or weight.dtype != torch.float32 or weight.shape != (W,) or not weight.is_contiguous() \
+                or out.shape != x.shape or not out.is_contiguous():
+            raise KernelError("gated_group_norm: x float32 [T, W], gate [T, W], weight float32 [W], out [T, W]")
+        self.launches += 1
+        _check(self.lib.chibi_gated_group_norm(_ptr(x), _ptr(gate), _code(gate), gate.stride(0), _ptr(weight),
+                                               _ptr(out), _code(out), T, W // group, group, float(eps),
+                                               self._stream()), "gated_group_norm")
+
+    def scale(self, x: torch.Tensor, factor: float) -> None:
+        """x *= factor, in place (float32)."""
+        _need_cuda(x)
+        if x.dtype != torch.float32 or not x.is_contiguous():
+            raise KernelError("scale: x must be contiguous float32")
+        self.launches += 1
+        _check(self.lib.chibi_scale(_ptr(x), float(factor), x.numel(), self._stream()), "scale")
+
+    def cast_rows(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        """out = x in out's type; both [rows, n], rows may be strided."""
+        _need_cuda(x, out)
+        _rows_contiguous(x, "cast_rows: x")
+        _rows_contiguous(out, "cast_rows: out")
+        if x.shape != out.shape:
+            raise KernelError("cast_rows: shapes")
+        self.launches += 1
+        _check(self.lib.chibi_cast_rows(_ptr(x), _code(x), x.stride(0), _ptr(out), _code(out), out.stride(0),
+                                        x.shape[0], x.shape[1], self._stream()), "cast_rows")
+
+    def add_row_vector(self, acc: torch.Tensor, vec: torch.Tensor) -> None:
+        """acc[r, :] += vec for every row (both float32)."""
+        _need_cuda(acc, vec)
+        _rows_contiguous(acc, "add_row_vector: acc")
+        if acc.dtype != torch.float32 or vec.dtype != torch.float32 or vec.shape != (acc.shape[1],) \
+                or not vec.is_contiguous():
+            raise KernelError("add_row_vector: acc float32 [rows, n] and vec float32 [n]")
+        self.launches += 1
+        _check(self.lib.chibi_add_row_vector(_ptr(acc), acc.stride(0), _ptr(vec), acc.shape[0], acc.shape[1],
+                                             self._stream()), "add_row_vector")
+
+    ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+    def activation(self, x: torch.Tensor, kind: str) -> None:
+        """x = act(x) in place, computed in 32-bit."""
+        _need_cuda(x)
+        if not x.is_contiguous() or kind not in self.ACTIVATIONS:
+            raise KernelError(f"activation: contiguous x and one of {sorted(self.ACTIVATIONS)}")
+        self.launches += 1
+        _check(self.lib.chibi_activation(_ptr(x), _code(x), x.numel(), self.ACTIVATIONS[kind], self._stream()),
+               "activation")
+
+    def linear_activation(self, x, w: torch.Tensor, out: torch.Tensor, kind: str) -> bool:
+        """out = act(x @ w^T) with the activation applied to the 32-bit sums: by the
+        kernel that adds up a split product (few rows).  False if this product is not
+        one that is split; nothing has run then."""
+        if kind not in self.ACTIVATIONS:
+            raise KernelError(f"linear_activation: one of {sorted(self.ACTIVATIONS)}")
+        pending = self.linear_partial(x, w)
+        if pending is None:
+            return False
+        if not out.is_contiguous() or out.shape != (pending.M, pending.N):
+            raise KernelError("linear_activation: out must be contiguous [M, N]")
+        self.launches += 1
+        _check(self.lib.chibi_reduce_activation(_ptr(pending.partial), pending.splits, pending.M * pending.N,
+                                                _ptr(out), _code(out), self.ACTIVATIONS[kind], self._stream()),
+               "reduce_activation")
+        return True
 
     def gather_rows(self, x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
         _need_cuda(x, rows, out)

@@ -1,0 +1,71 @@
+"""Adapters: parts outside the blocks.
+
+"scale": multiplies its argument by a constant (``params``: "factor"); as an
+input adapter it scales the embeddings, as a logit adapter the logits.
+
+"reentry_mix": a stream adapter for a group of layers that runs several times.
+Before each pass the residual x is replaced by W [x; x0] + step[turn], where x0
+is the residual as the input adapters left it, W is [hidden, 2 * hidden] (x's
+columns first) and step holds one vector per pass (tensor roles "mix", "step").
+The product takes its inputs in the activations' type; the sum is 32-bit.
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .base import Adapter, Runtime, TensorSpec, register_adapter
+
+
+class Scale(Adapter):
+    def __init__(self, spec, runtime: Runtime):
+        self.factor = float(spec.constants()["factor"])
+        self.runtime = runtime
+
+    def launch_key(self, ctx):
+        return ()
+
+    def forward(self, x: torch.Tensor, ctx, turn: int = 0) -> None:
+        if self.factor != 1.0:
+            self.runtime.kernels.scale(x, self.factor)
+
+
+class ReentryMix(Adapter):
+    needs_embedding_output = True
+
+    def __init__(self, spec, runtime: Runtime):
+        self.names = spec.names()
+        c = spec.constants()
+        self.hidden, self.turns = int(c["hidden_size"]), int(c["turns"])
+        self.runtime = runtime
+        self.mix: torch.Tensor = None
+        self.step: torch.Tensor = None
+
+    def expected_tensors(self) -> List[TensorSpec]:
+        return [TensorSpec(self.names["mix"], (self.hidden, 2 * self.hidden)),
+                TensorSpec(self.names["step"], (self.turns, self.hidden), init=("normal", 0.0, 0.1))]
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.mix = tensors[self.names["mix"]].contiguous()
+        self.step = tensors[self.names["step"]].float().contiguous()
+
+    def launch_key(self, ctx):
+        return ()
+
+    def forward(self, x: torch.Tensor, ctx, turn: int = 0) -> None:
+        rt = self.runtime
+        k = rt.kernels
+        T, D = x.shape
+        both = ctx.workspace.get("reentry.both", (T, 2 * D), rt.dtype)
+        if ctx.shared.get("reentry.filled") is not both:
+            # x0 is the same in every pass of a step: its half is filled once
+            k.cast_rows(ctx.shared["embedding output"], both[:, D:])
+            ctx.shared["reentry.filled"] = both
+        k.cast_rows(x, both[:, :D])
+        k.linear(both, self.mix, x)
+        k.add_row_vector(x, self.step[turn])
+
+
+register_adapter("scale", Scale, replace=True)
+register_adapter("reentry_mix", ReentryMix, replace=True)

@@ -11,6 +11,12 @@ The part takes every size and constant from its spec: head counts, head size,
 scale, window, the norm of q and k (or none), the position encoding (or none).
 When its run step reads another step's cache, it computes q only and appends
 nothing.
+
+Options of the spec beyond that: a soft cap of the scores (c * tanh(s / c)), a
+bias by distance taken off the capped score (r1[h] * ln(1 + r2[h] * (i - j)),
+two learned numbers per query head, kept in 32-bit), and values tied to the
+keys (one product gives q | k, the cache holds keys only and the kernels read
+them as values too).
 """
 from __future__ import annotations
 
@@ -33,24 +39,36 @@ class PagedAttention(Mixer):
         self.o_proj: torch.Tensor = None
         self.q_norm: torch.Tensor = None
         self.k_norm: torch.Tensor = None
+        self.distance_r1: torch.Tensor = None
+        self.distance_r2: torch.Tensor = None
+        if spec.distance_bias not in (None, "log"):
+            raise ValueError(f"distance bias '{spec.distance_bias}' is not supported (None or 'log')")
+        self.kv_arrays = 1 if spec.tied_values else 2
 
     # ---- weights
     def expected_tensors(self) -> List[TensorSpec]:
         s = self.spec
         qw, kw = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
         out = [TensorSpec(self.names["q_proj"], (qw, s.hidden_size)),
-               TensorSpec(self.names["k_proj"], (kw, s.hidden_size)),
-               TensorSpec(self.names["v_proj"], (kw, s.hidden_size)),
-               TensorSpec(self.names["o_proj"], (s.hidden_size, qw))]
+               TensorSpec(self.names["k_proj"], (kw, s.hidden_size))]
+        if not s.tied_values:
+            out.append(TensorSpec(self.names["v_proj"], (kw, s.hidden_size)))
+        out.append(TensorSpec(self.names["o_proj"], (s.hidden_size, qw)))
+        if s.distance_bias is not None:
+            out += [TensorSpec(self.names["distance_r1"], (s.num_heads,), init=("uniform", 0.0, 2.0)),
+                    TensorSpec(self.names["distance_r2"], (s.num_heads,), init=("uniform", 0.1, 0.5))]
         if s.qk_norm is not None:
             out += [TensorSpec(self.names["q_norm"], (s.qk_norm.size,)),
                     TensorSpec(self.names["k_norm"], (s.qk_norm.size,))]
         return out
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        q, k, v = (tensors[self.names[r]] for r in ("q_proj", "k_proj", "v_proj"))
-        k, v = k.to(q.dtype), v.to(q.dtype)
-        self.qkv = torch.cat([q, k, v], dim=0).contiguous()
+        roles = ("q_proj", "k_proj") if self.spec.tied_values else ("q_proj", "k_proj", "v_proj")
+        mats = [tensors[self.names[r]] for r in roles]
+        self.qkv = torch.cat([m.to(mats[0].dtype) for m in mats], dim=0).contiguous()
+        if self.spec.distance_bias is not None:
+            self.distance_r1 = tensors[self.names["distance_r1"]].float().contiguous()
+            self.distance_r2 = tensors[self.names["distance_r2"]].float().contiguous()
         self.o_proj = tensors[self.names["o_proj"]].contiguous()
         if self.spec.qk_norm is not None:
             self.q_norm = tensors[self.names["q_norm"]].contiguous()
@@ -61,7 +79,8 @@ class PagedAttention(Mixer):
 
     def cache_need(self):
         s = self.spec
-        return PagedKVNeed(num_kv_heads=s.num_kv_heads, head_dim=s.head_dim, window=s.window)
+        return PagedKVNeed(num_kv_heads=s.num_kv_heads, head_dim=s.head_dim, window=s.window,
+                           tied_values=s.tied_values)
 
     def launch_key(self, ctx):
         if self.position.fused_rotation() is None:
@@ -81,7 +100,8 @@ class PagedAttention(Mixer):
         nq, nkv, d = s.num_heads, s.num_kv_heads, s.head_dim
         qw, kw = nq * d, nkv * d
         writes = cache.writes
-        width = qw + 2 * kw if writes else qw
+        width = qw + self.kv_arrays * kw if writes else qw
+        modified = s.softcap is not None or s.distance_bias is not None
         fused = self.position.fused_rotation()
         if fused is not None and fused[0] is not None and self._heads_from_the_product(x, ctx, cache, fused):
             return self._attend(residual, ctx, cache)
@@ -102,7 +122,8 @@ class PagedAttention(Mixer):
         k_norm_w = self.k_norm if norm is not None else None
         att = ctx.workspace.get("attn.out", (T, qw), rt.dtype)
         from_partial = getattr(k, "attention_decode_from_partial", None)
-        if pending is not None and ctx.max_q_len == 1 and from_partial is not None and fused[0] is not None:
+        if pending is not None and ctx.max_q_len == 1 and from_partial is not None and fused[0] is not None \
+                and not modified and not s.tied_values:
             # every sequence brings one token: the attention kernel finishes the product itself
             if from_partial(pending, cache.keys, cache.values, att, table, ctx.q_start, ctx.ctx_len, nq, nkv, d,
                             cache.page_size, s.scale, s.window, ctx.max_ctx_len, q_norm_w, k_norm_w, fused[0],
@@ -124,7 +145,7 @@ class PagedAttention(Mixer):
         inv_freq, rotary_dim = fused
         (k.qk_norm_rope_append_partial if pending is not None else k.qk_norm_rope_append)(
             pending if pending is not None else qkv, q, cache.keys if writes else None,
-            cache.values if writes else None,
+            cache.values if writes and not s.tied_values else None,
             q_norm_w, k_norm_w, inv_freq, rotary_dim, norm.eps if norm is not None else 0.0,
             norm.weight_offset if norm is not None else 0.0,
             ctx.positions, ctx.seq_of_token, table if writes else None, nq, nkv, d, cache.page_size,
@@ -140,9 +161,13 @@ class PagedAttention(Mixer):
         T = ctx.num_tokens
         q = ctx.workspace.get("attn.q", (T, nq * d), rt.dtype)
         att = ctx.workspace.get("attn.out", (T, nq * d), rt.dtype)
+        extra = {}
+        if s.softcap is not None or s.distance_bias is not None:
+            extra = {"softcap": s.softcap, "distance_bias": (self.distance_r1, self.distance_r2)
+                     if s.distance_bias is not None else None}
         k.attention(q, cache.keys, cache.values, att, ctx.tables[cache.group], ctx.q_start, ctx.ctx_len,
                     ctx.seq_of_token, ctx.positions, nq, nkv, d, cache.page_size, s.scale,
-                    s.window, ctx.max_q_len, ctx.max_ctx_len, ctx.min_q_len, ctx.seq_rows)
+                    s.window, ctx.max_q_len, ctx.max_ctx_len, ctx.min_q_len, ctx.seq_rows, **extra)
         return k.linear(att, self.o_proj, residual, residual=residual, defer=True)
 
     def _heads_from_the_product(self, x, ctx, cache, fused) -> bool:
@@ -155,7 +180,7 @@ class PagedAttention(Mixer):
         takes = getattr(k, "finishes_heads", None)
         T = ctx.num_tokens
         nq, nkv, d = s.num_heads, s.num_kv_heads, s.head_dim
-        if takes is None or not takes(T, d, fused[1], rt.dtype):
+        if takes is None or s.tied_values or not takes(T, d, fused[1], rt.dtype):
             return False
         cos_sin = self.position.step_table(ctx)
         if cos_sin is None:

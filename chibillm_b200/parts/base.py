@@ -39,23 +39,29 @@ class TensorSpec:
     name: str
     shape: Tuple[int, ...]
     kind: str = "float"          # "float" (kept bfloat16 / 32-bit) or "int" (kept int32)
+    # how a random model fills it: None (matrices N(0, 0.02), vectors 1 + U(-0.1, 0.1)), or
+    # ("uniform", low, high) / ("normal", mean, std)
+    init: Optional[Tuple[str, float, float]] = None
 
 
 # ------------------------------------------------------------------ cache needs
 @dataclass(frozen=True)
 class PagedKVNeed:
     """Keys and values of every position, in pages; ``window`` None = all keys
-    stay, an integer = only that many most recent ones are ever read."""
+    stay, an integer = only that many most recent ones are ever read.
+    ``tied_values``: the values are the keys; the pool holds one array."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    tied_values: bool = False
 
 
 @dataclass(frozen=True)
 class FixedStateNeed:
     """Per-request state of fixed size: named arrays, zeroed when a request is
-    admitted.  ``arrays``: ((name, shape, dtype), ...)."""
+    admitted.  ``arrays``: ((name, shape, dtype), ...); a dtype of None stands for
+    the type of the run's activations."""
 
     arrays: Tuple[Tuple[str, Tuple[int, ...], torch.dtype], ...]
 
@@ -156,6 +162,12 @@ class Block(Part):
 
     mixer: Mixer
 
+    def cache_need(self):
+        """What a run of this block keeps per request: its mixer's need, or a tuple
+        of needs when other parts of the block keep something too (the block's
+        ``forward`` then gets a tuple of views in the same order)."""
+        return self.mixer.cache_need()
+
     def forward(self, residual: torch.Tensor, ctx, cache, pending=None):
         """``pending``: what the block before left to be added to the residual.
         Returns what this block leaves pending (or None)."""
@@ -163,12 +175,18 @@ class Block(Part):
 
 
 class Adapter(Part):
-    """A part at one of the decoder's ends (AdapterSpec).  An input adapter gets
-    the 32-bit residual [T, hidden] right after the token embedding, a logit
-    adapter the 32-bit logits [R, vocab] of the wanted rows; both change their
-    argument in place.  ``ctx`` is the step's context (positions, sequences)."""
+    """A part outside the blocks (AdapterSpec).  An input adapter gets the 32-bit
+    residual [T, hidden] right after the token embedding, a logit adapter the
+    32-bit logits [R, vocab] of the wanted rows, a stream adapter the 32-bit
+    residual right before the run step that names it, with that step's ``turn``;
+    all change their argument in place.  ``ctx`` is the step's context
+    (positions, sequences); a stream adapter that sets ``needs_embedding_output``
+    finds the residual as it stood after the input adapters under
+    ``ctx.shared["embedding output"]``."""
 
-    def forward(self, x: torch.Tensor, ctx) -> None:
+    needs_embedding_output = False
+
+    def forward(self, x: torch.Tensor, ctx, turn: int = 0) -> None:
         raise NotImplementedError
 
 

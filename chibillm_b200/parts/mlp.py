@@ -63,4 +63,46 @@ class GatedMLP(FeedForward):
         return k.linear(act, self.down, residual, residual=residual, defer=True)
 
 
+class DenseMLP(FeedForward):
+    """Dense feed-forward without a gate: residual += down(act(up(x))).  The
+    activation is applied to the 32-bit sums of the first product (by the kernel
+    that adds up a split product, or in place on the product's output)."""
+
+    ACTIVATIONS = ("gelu", "gelu_tanh", "silu", "relu")
+
+    def __init__(self, spec, names: Dict[str, str], runtime: Runtime):
+        if spec.activation not in self.ACTIVATIONS:
+            raise ValueError(f"activation '{spec.activation}' is not supported by mlp; known: {self.ACTIVATIONS}")
+        self.spec = spec
+        self.names = names
+        self.runtime = runtime
+        self.up: torch.Tensor = None
+        self.down: torch.Tensor = None
+
+    def expected_tensors(self) -> List[TensorSpec]:
+        s = self.spec
+        return [TensorSpec(self.names["up_proj"], (s.intermediate_size, s.hidden_size)),
+                TensorSpec(self.names["down_proj"], (s.hidden_size, s.intermediate_size))]
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.up = tensors[self.names["up_proj"]].contiguous()
+        self.down = tensors[self.names["down_proj"]].contiguous()
+
+    accepts_scaled_rows = True       # x goes to the up product and nowhere else
+
+    def launch_key(self, ctx):
+        return ()
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx) -> None:
+        k = self.runtime.kernels
+        T = x.shape[0]
+        act = ctx.workspace.get("mlp.act", (T, self.spec.intermediate_size), self.runtime.dtype)
+        fused = getattr(k, "linear_activation", None)
+        if fused is None or not fused(x, self.up, act, self.spec.activation):
+            k.linear(x, self.up, act)
+            k.activation(act, self.spec.activation)
+        return k.linear(act, self.down, residual, residual=residual, defer=True)
+
+
 register_feed_forward("gated_mlp", GatedMLP, replace=True)
+register_feed_forward("mlp", DenseMLP, replace=True)

@@ -1,7 +1,8 @@
 """Random weights from a configuration and a seed.
 
 Matrices and the embedding table are N(0, 0.02); vectors (norm weights, the
-per-head norms of q and k included) are 1 + U(-0.1, 0.1).  The generator is
+per-head norms of q and k included) are 1 + U(-0.1, 0.1); a part may name
+another distribution for a tensor (``TensorSpec.init``: biases, rates).  The generator is
 counter based: the value of element ``i`` of a tensor depends only on (seed,
 tensor name, i), through integer mixing (the splitmix64 finaliser) and a
 Box-Muller step in 64-bit floats, so the same values come out on the CPU and
@@ -57,7 +58,7 @@ def _key(seed: int, name: str) -> int:
     return _signed(int.from_bytes(digest[:8], "little"))
 
 
-def _fill(out: torch.Tensor, key: int, normal: bool) -> None:
+def _fill(out: torch.Tensor, key: int, normal: bool, init=None) -> None:
     flat = out.view(-1)
     n = flat.numel()
     for start in range(0, n, _CHUNK):
@@ -65,10 +66,13 @@ def _fill(out: torch.Tensor, key: int, normal: bool) -> None:
         bits = _mix(torch.arange(start + 1, stop + 1, dtype=torch.int64, device=out.device), key)
         hi = _lsr(bits, 32).to(torch.float64)
         u1 = (hi + 0.5) * (1.0 / 4294967296.0)
-        if normal:
+        if normal or (init is not None and init[0] == "normal"):
             lo = (bits & 0xFFFFFFFF).to(torch.float64)
             u2 = (lo + 0.5) * (1.0 / 4294967296.0)
-            v = torch.sqrt(-2.0 * torch.log(u1)) * torch.cos((2.0 * math.pi) * u2) * MATRIX_STD
+            v = torch.sqrt(-2.0 * torch.log(u1)) * torch.cos((2.0 * math.pi) * u2)
+            v = v * MATRIX_STD if init is None else init[1] + v * init[2]
+        elif init is not None:
+            v = init[1] + u1 * (init[2] - init[1])
         else:
             v = 1.0 + (2.0 * u1 - 1.0) * VECTOR_SPREAD
         flat[start:stop] = v.to(torch.float32).to(out.dtype)
@@ -79,7 +83,9 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype,
     if spec.kind == "int":
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
     t = torch.empty(spec.shape, dtype=dtype, device=device)
-    _fill(t, _key(seed, spec.name), normal=len(spec.shape) >= 2)
+    if spec.init is not None and spec.init[0] not in ("normal", "uniform"):
+        raise ValueError(f"tensor {spec.name}: unknown way to fill it, {spec.init!r}")
+    _fill(t, _key(seed, spec.name), normal=len(spec.shape) >= 2 and spec.init is None, init=spec.init)
     return t
 
 

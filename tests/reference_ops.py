@@ -76,18 +76,19 @@ class ReferenceKernels:
         if not append:
             return
         k = rotate(norm(qkv[:, qw:qw + kw].float().reshape(T, nkv, d), k_norm_w))
-        v = qkv[:, qw + kw:qw + 2 * kw].float().reshape(T, nkv, d)
         pos = positions.long()
         rows = seq_of_token.long() if seq_rows is None else seq_rows.long()[seq_of_token.long()]
         pages = block_table[rows, pos // page_size].long()
         assert (pages >= 0).all() and (pages < k_cache.shape[0]).all(), "append outside the pool"
         slots = pos % page_size
         k_cache[pages, :, slots, :] = k.to(k_cache.dtype)
-        v_cache[pages, :, slots, :] = v.to(v_cache.dtype)
+        if v_cache is not None:             # None: the values are the keys, the cache holds keys only
+            v = qkv[:, qw + kw:qw + 2 * kw].float().reshape(T, nkv, d)
+            v_cache[pages, :, slots, :] = v.to(v_cache.dtype)
 
     def attention(self, q, k_cache, v_cache, out, block_table, q_start, ctx_len, seq_of_token,
                   positions, nq, nkv, d, page_size, scale, window, max_q_len, max_ctx_len, min_q_len=0,
-                  seq_rows=None):
+                  seq_rows=None, softcap=None, distance_bias=None):
         self._count("attention")
         T = q.shape[0]
         group = nq // nkv
@@ -107,6 +108,11 @@ class ReferenceKernels:
             for h in range(nq):
                 g = h // group
                 sc = (keys[:, g, :] @ qf[t, h]) * scale
+                if softcap is not None:
+                    sc = softcap * torch.tanh(sc / softcap)
+                if distance_bias is not None:
+                    r1, r2 = distance_bias
+                    sc = sc - r1[h].float() * torch.log1p(r2[h].float() * (p - idx).float())
                 pr = torch.softmax(sc, dim=0)
                 res[t, h] = pr @ vals[:, g, :]
         out.copy_(res.reshape(T, nq * d).to(out.dtype))
@@ -123,6 +129,80 @@ class ReferenceKernels:
         inter = out.shape[1]
         g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
         out.copy_(((g / (1.0 + torch.exp(-g))) * u).to(out.dtype))
+
+    def scale(self, x, factor):
+        self._count("scale")
+        x.mul_(factor)
+
+    def cast_rows(self, x, out):
+        out.copy_(x.to(out.dtype))
+
+    def add_row_vector(self, acc, vec):
+        acc.add_(vec.float()[None, :])
+
+    def activation(self, x, kind):
+        self._count("activation")
+        z = x.float()
+        if kind == "gelu":
+            y = 0.5 * z * (1.0 + torch.erf(z / math.sqrt(2.0)))
+        elif kind == "gelu_tanh":
+            y = 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
+        elif kind == "silu":
+            y = z / (1.0 + torch.exp(-z))
+        elif kind == "relu":
+            y = torch.clamp(z, min=0.0)
+        else:
+            raise ValueError(kind)
+        x.copy_(y.to(x.dtype))
+
+    def short_conv(self, x, weight, history, out, q_start, positions, state_slots, max_q_len):
+        """y_t = x_t + sum_j w[:, j] x_(t - taps + 1 + j); what lies before a step's
+        first token comes from ``history`` [slots, taps - 1, D] (oldest first), which
+        then takes the sequence's last taps - 1 inputs."""
+        self._count("short_conv")
+        taps = weight.shape[1]
+        keep = taps - 1
+        for s in range(state_slots.numel()):
+            a, b = int(q_start[s]), int(q_start[s + 1])
+            slot = int(state_slots[s])
+            past = history[slot, :keep].float() if keep else x.new_zeros((0, x.shape[1])).float()
+            seq = torch.cat([past, x[a:b].float()], dim=0)
+            y = x[a:b].float().clone()
+            for j in range(taps):
+                y = y + weight[:, j].float() * seq[j:j + (b - a)]
+            out[a:b] = y.to(out.dtype)
+            if keep:
+                history[slot, :keep] = seq[seq.shape[0] - keep:].to(history.dtype)
+
+    def delta_rule(self, proj, decay_out, decay_bias, removal_bias, state, o, q_start, state_slots, heads, d,
+                   rank, decay_scale, key_eps, max_q_len):
+        """proj [T, 5 * heads * d + rank] = r | k | v | gate | removal | low; state
+        [slots, heads, d, d] (key rows, value columns); o [T, heads * d] 32-bit."""
+        self._count("delta_rule")
+        W = heads * d
+        p = proj.float()
+        low = torch.tanh(p[:, 5 * W:5 * W + rank])
+        decay = torch.exp(-decay_scale * torch.sigmoid(low @ decay_out.float().t() + decay_bias.float()))
+        rate = torch.sigmoid(p[:, 4 * W:5 * W] + removal_bias.float())
+        for s in range(state_slots.numel()):
+            slot = int(state_slots[s])
+            for t in range(int(q_start[s]), int(q_start[s + 1])):
+                for h in range(heads):
+                    c = slice(h * d, (h + 1) * d)
+                    r, k, v = p[t, c], p[t, W + h * d:W + (h + 1) * d], p[t, 2 * W + h * d:2 * W + (h + 1) * d]
+                    u = k / torch.sqrt((k * k).sum() + key_eps)
+                    S = state[slot, h]
+                    S = decay[t, c][:, None] * S - torch.outer(rate[t, c] * u, u @ S) + torch.outer(k, v)
+                    state[slot, h] = S
+                    o[t, c] = S.t() @ r
+
+    def gated_group_norm(self, x, gate, weight, eps, group, out):
+        """out = x / rms(x over each run of ``group`` features) * weight * sigmoid(gate)."""
+        self._count("gated_group_norm")
+        T, W = x.shape
+        xf = x.float().view(T, W // group, group)
+        y = xf / torch.sqrt((xf * xf).mean(-1, keepdim=True) + eps)
+        out.copy_((y.view(T, W) * weight.float() * torch.sigmoid(gate.float())).to(out.dtype))
 
     def gather_rows(self, x, rows, out):
         self._count("gather_rows")
