@@ -15,6 +15,9 @@ its time, against the measured copy bandwidth; ``points`` decode at batch 1 and
 filled by real prefill steps for the end-to-end run and with random values for
 the device-timed runs (the work of a decode step does not depend on the values).
 
+``--design gitipel`` prints, instead of the record, prefill and decode of the
+Gitipel design beside Qwen3 at equal layer sizes, with the time of every kernel.
+
 ``--timeline`` prints, instead of the record, when the CTAs of every kernel of one
 decode step started, waited and ended.  ``--shape`` runs the same at the Qwen3-0.6B or
 Qwen3-14B layer sizes, and
@@ -373,6 +376,106 @@ def measure_products(cfg, rows, seconds=2.0):
             "unit": "TFLOP/s", "rows": rows, "products": out, "n_gpus": 1, "dtype": "bf16", "data": "synthetic"}
 
 
+# ------------------------------------------------------------------ another design beside Qwen3
+# Layer sizes for ``--design gitipel``: (width, attention heads, kv heads, head size, feed-forward).
+DESIGN_SIZES = {"small": (1024, 16, 8, 64, 3072), "medium": (2048, 16, 8, 128, 6144),
+                "large": (4096, 32, 8, 128, 12288)}
+
+
+def gitipel_config(width, heads, kv_heads, dim, ff, vocab=32768):
+    """Four layers, attention and delta rule in turn, the first two run twice: six layer
+    runs.  Delta-rule heads of 64 channels over the whole width, a decay input of rank 64."""
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim,
+                                          "scale": dim ** -0.5, "softcap": 50.0}, "mlp": {"kind": "dense", "ff": ff}}
+    rec = {"type": "general_delta", "mixer": {"heads": width // 64, "dim": 64, "rank": 64},
+           "mlp": {"kind": "dense", "ff": ff}}
+    return {"architecture": "Gitipel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0}, "logit_scale": 1.0, "canon": {"taps": 4},
+            "layers": [att, rec, att, rec], "loop": {"start": 0, "stop": 2, "times": 2}}
+
+
+def qwen3_config_like(width, heads, kv_heads, dim, ff, layers=6, vocab=32768):
+    cfg = dict(QWEN3_8B)
+    cfg.update(num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv_heads,
+               head_dim=dim, intermediate_size=ff, vocab_size=vocab)
+    return cfg
+
+
+def measure_design(name, cfg, vocab, prompt_tokens, batch, held, steps, warmup, profile_steps=4):
+    """Prefill of one prompt and decode steps of ``batch`` requests that hold ``held``
+    tokens, device-timed; then the same under the launch profiler (every launch timed
+    alone), for the share of each kernel."""
+    import torch
+    from chibillm_b200.engine.batch import StepEntry
+    from chibillm_b200.engine.runner import ModelRunner
+    from chibillm_b200.sampling import Sampler
+
+    pool = ((batch * (held + warmup + steps + profile_steps + 80) + prompt_tokens + 127) // 64) * 64
+    runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", page_size=16, pool_tokens=pool,
+                                     max_requests=batch + 1)
+    for group in runner.storage.keys:
+        runner.storage.keys[group].normal_(0.0, 0.5)
+        if runner.storage.values[group] is not runner.storage.keys[group]:
+            runner.storage.values[group].normal_(0.0, 0.5)
+    sampler = Sampler(runner.runtime)
+    median, fastest = measure_prefill(runner, prompt_tokens, vocab, repeats=5)
+    dec = measure_decode(runner, sampler, batch, held, steps, warmup, vocab, name)
+    out = {"prefill_ms": round(median, 3), "prefill_ms_fastest": round(fastest, 3),
+           "prefill_tok_s": round(prompt_tokens / (median / 1e3)), "decode_ms_per_step": round(dec["ms_per_step"], 4),
+           "decode_tok_s": round(dec["tok_s"]), "decode_launches_per_step": dec["launches"] // steps}
+    # per kernel: a prompt step and a few decode steps with every launch timed alone
+    profiler = runner.runtime.kernels.enable_profiling()
+    g = torch.Generator().manual_seed(3)
+
+    def table(reset=True):
+        profiler._collect()
+        rows = {k: {"calls": int(v[0]), "avg_us": round(v[1] * 1e3 / v[0], 2), "total_us": round(v[1] * 1e3, 1)}
+                for k, v in sorted(profiler.totals.items(), key=lambda kv: -kv[1][1])}
+        if reset:
+            profiler.totals.clear()
+        return rows
+
+    runner.step([StepEntry("p", torch.randint(0, vocab, (prompt_tokens,), generator=g).tolist(), [prompt_tokens - 1])])
+    runner.end("p")
+    table()                                   # the first run under the profiler warms up
+    runner.step([StepEntry("p", torch.randint(0, vocab, (prompt_tokens,), generator=g).tolist(), [prompt_tokens - 1])])
+    runner.end("p")
+    out["prefill_kernels"] = table()
+    ids = [f"{name}q{i}" for i in range(batch)]
+    for rid in ids:
+        fill_request(runner, rid, held)
+    for i in range(profile_steps + 1):
+        runner.step([StepEntry(rid, [int(t)], [0]) for rid, t in zip(ids, torch.randint(0, vocab, (batch,), generator=g))])
+        if i == 0:
+            table()
+    rows = table()
+    for r in rows.values():
+        r["calls"] //= profile_steps
+        r["total_us"] = round(r["total_us"] / profile_steps, 1)
+    out["decode_kernels"] = rows
+    for rid in ids:
+        runner.end(rid)
+    del runner
+    torch.cuda.empty_cache()
+    return out
+
+
+def compare_designs(sizes, prompt_tokens, batch, held, steps, warmup):
+    """Gitipel beside Qwen3 at equal layer sizes (six layer runs each, random weights)."""
+    result = {"metric": "prefill and decode of Gitipel beside Qwen3 at equal layer sizes", "layer_runs": 6,
+              "prompt_tokens": prompt_tokens, "decode_batch": batch, "decode_tokens_held": held, "dtype": "bf16",
+              "data": "synthetic", "sizes": {}}
+    for size in sizes:
+        width, heads, kv_heads, dim, ff = DESIGN_SIZES[size]
+        entry = {"width": width, "heads": heads, "kv_heads": kv_heads, "head_dim": dim, "ff": ff}
+        entry["gitipel"] = measure_design("g", gitipel_config(width, heads, kv_heads, dim, ff), 32768, prompt_tokens,
+                                          batch, held, steps, warmup)
+        entry["qwen3"] = measure_design("q", qwen3_config_like(width, heads, kv_heads, dim, ff), 32768, prompt_tokens,
+                                        batch, held, steps, warmup)
+        result["sizes"][size] = entry
+    return result
+
+
 def print_timeline(cfg, batch, held, prompt_tokens=0):
     """One decode step, replayed from its CUDA graph, as its CTAs saw it: for every launch when
     its first and last CTA started, when their wait for the launch before ended and when they
@@ -450,6 +553,11 @@ def main() -> int:
     ap.add_argument("--check-tokens", type=int, default=0,
                     help="with --mixed-requests: also generate this many tokens of every request with the 32-bit "
                          "engine under two budgets and report how the runs agree")
+    ap.add_argument("--design", default=None, choices=["gitipel"],
+                    help="instead of the record: prefill and decode of this design beside Qwen3 at equal layer "
+                         "sizes (--design-sizes), with the time of every kernel")
+    ap.add_argument("--design-sizes", default="small,medium,large",
+                    help="layer sizes for --design, with commas between them: " + ", ".join(DESIGN_SIZES))
     ap.add_argument("--shape", default="qwen3-8b", choices=sorted(SHAPES),
                     help="layer sizes (random weights); the contract's record is the default")
     args = ap.parse_args()
@@ -476,6 +584,15 @@ def main() -> int:
     cfg["num_hidden_layers"] = layers
     vocab = cfg["vocab_size"]
     peaks, peaks_src = load_peaks()
+    if args.design is not None:
+        sizes = [x for x in args.design_sizes.split(",") if x]
+        unknown = [x for x in sizes if x not in DESIGN_SIZES]
+        if unknown:
+            print(f"unknown --design-sizes {unknown}; known: {sorted(DESIGN_SIZES)}")
+            return 2
+        print(json.dumps(compare_designs(sizes, args.prefill_tokens, args.batch, args.prompt, min(args.steps, 64),
+                                         args.warmup)), flush=True)
+        return 0
     if args.products:
         print(json.dumps(measure_products(cfg, args.prefill_tokens)), flush=True)
         return 0

@@ -44,6 +44,8 @@ struct GemmParams {
     float* partial;        // [splits][M][N] when the K range is split through global memory, else null
     int swiglu;            // the rows of w come in blocks of 64 gate rows then 64 up rows; out[M, N / 2] =
                            // silu(gate) * up
+    int act;               // 0: none; k > 0: activation k - 1 (see activate()) on the sums where they become
+                           // the output's type (no residual with it)
     int* error;
     // Many rows (the persistent kernel): the last sk_tiles output tiles do not fill a round of all
     // CTAs, so the other CTAs help with them.  CTA i < sk_tiles takes the first sk_head K blocks of
@@ -94,12 +96,16 @@ struct GemmSmem {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 };
 
+__device__ __noinline__ float activate_out_of_line(float v, int kind) { return activate(v, kind); }
+
 __device__ __forceinline__ void store_value(const GemmParams& p, int m, int n, float v)
 {
     if (m >= p.M || n >= p.N)
         return;
     if (p.residual)
         v = p.residual[(size_t)m * p.res_stride + n] + v;
+    else if (p.act)
+        v = activate_out_of_line(v, p.act - 1);
     if (p.out_type == CHIBI_F32)
         static_cast<float*>(p.out)[(size_t)m * p.out_stride + n] = v;
     else
@@ -298,7 +304,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                 const int m = a_row;
                 const bool vec = m < p.M && b_row0 + CHUNK <= p.N && (p.out_stride % 8 == 0)
                     && (!p.residual || p.res_stride % 4 == 0);
-                if (vec && p.out_type == CHIBI_F32) {
+                if (vec && p.out_type == CHIBI_F32 && !p.act) {
                     float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + (size_t)m * p.out_stride + b_row0);
                     const float4* res = p.residual
                         ? reinterpret_cast<const float4*>(p.residual + (size_t)m * p.res_stride + b_row0)
@@ -313,7 +319,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                         }
                         dst[j] = v;
                     }
-                } else if (vec && p.out_type == CHIBI_BF16 && !p.residual) {
+                } else if (vec && p.out_type == CHIBI_BF16 && !p.residual && !p.act) {
                     uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.out_stride + b_row0);
 #pragma unroll
                     for (int j = 0; j < CHUNK / 8; ++j) {
@@ -515,6 +521,44 @@ __device__ __forceinline__ void epilogue_heads(const GemmParams& p, uint32_t tad
     }
 }
 
+// The bfloat16 output with an activation on the sums (factor of the row first).  Kept out of
+// line: the products without an activation keep their registers.
+template <int BN>
+__device__ __noinline__ void epilogue_rows_activated(const GemmParams& p, uint32_t taddr, int m0, int lane,
+                                                     int tile_b, uint8_t* stage, float inv)
+{
+    const int sub = lane >> 3, unit = lane & 7;
+    const int kind = p.act - 1;
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 64) {
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+            uint32_t r32[32];
+            tmem_load_32x32(taddr + c0 + 32 * h, r32);
+            tmem_load_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 v[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    v[q] = __floats2bfloat162_rn(activate(inv * __uint_as_float(r32[8 * j + 2 * q]), kind),
+                                                 activate(inv * __uint_as_float(r32[8 * j + 2 * q + 1]), kind));
+                *stage_unit(stage, lane, 4 * h + j) = *reinterpret_cast<uint4*>(v);
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + sub;
+            const uint4 v = *stage_unit(stage, r, unit);
+            if (m0 + r < p.M)
+                *reinterpret_cast<uint4*>(out + (size_t)(m0 + r) * p.out_stride + tile_b * BN + c0 + unit * 8) = v;
+        }
+        __syncwarp();
+    }
+}
+
 template <int BN>
 __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_t taddr, int m0, int lane,
                                                     int tile_b, uint8_t* stage, const float* head_w = nullptr)
@@ -678,6 +722,10 @@ __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_
         }
         return;
     }
+    if (p.act && p.out_type == CHIBI_BF16 && !p.residual && inside && p.out_stride % 8 == 0) {
+        epilogue_rows_activated<BN>(p, taddr, m0, lane, tile_b, stage, inv);
+        return;
+    }
     if (p.out_type == CHIBI_BF16 && !p.residual && inside && p.out_stride % 8 == 0) {
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
 #pragma unroll 1
@@ -716,7 +764,7 @@ __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_
         tmem_load_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j)
-            store_value(p, m, tile_b * BN + c0 + j, __uint_as_float(r[j]));
+            store_value(p, m, tile_b * BN + c0 + j, inv * __uint_as_float(r[j]));
         __syncwarp();
     }
 }
@@ -1717,6 +1765,10 @@ CHIBI_API int chibi_gemm_bf16_fused(const void* x, const void* w, void* out, int
         return CHIBI_ERR_ARGUMENT;
     if (epilogue == 1 && (N % 128 != 0 || out_type != CHIBI_BF16 || residual))
         return CHIBI_ERR_UNSUPPORTED;
+    if (epilogue < 0 || epilogue > 5)
+        return CHIBI_ERR_ARGUMENT;
+    if (epilogue >= 2 && (out_type != CHIBI_BF16 || residual))
+        return CHIBI_ERR_UNSUPPORTED;      // epilogue 2 .. 5: activation 0 .. 3 on the sums, bfloat16 out
     GemmParams p {};
     p.K = K;
     p.M = M;
@@ -1728,6 +1780,7 @@ CHIBI_API int chibi_gemm_bf16_fused(const void* x, const void* w, void* out, int
     p.res_stride = res_stride;
     p.error = error;
     p.swiglu = epilogue == 1 ? 1 : 0;
+    p.act = epilogue >= 2 ? epilogue - 1 : 0;
     p.k_blocks_total = (K + TILE_K - 1) / TILE_K;
     CUtensorMap ma, mb;
     if (M <= 64)
@@ -1811,6 +1864,10 @@ CHIBI_API int chibi_gemm_bf16_rows(const void* x, const void* w, void* out, int 
         || (reinterpret_cast<uintptr_t>(out) & 15) || (residual && (reinterpret_cast<uintptr_t>(residual) & 15)))
         return CHIBI_ERR_UNSUPPORTED;
     const int bn = many_rows_tile_width(M, N, K);
+    if (epilogue < 0 || epilogue > 5)
+        return CHIBI_ERR_ARGUMENT;
+    if (epilogue >= 2 && (out_type != CHIBI_BF16 || residual || norm || heads))
+        return CHIBI_ERR_UNSUPPORTED;      // epilogue 2 .. 5: activation 0 .. 3 on the sums, bfloat16 out
     if (heads) {
         const bool caches = heads->k_cache != nullptr;
         if (epilogue != 0 || norm || residual)
@@ -1834,6 +1891,7 @@ CHIBI_API int chibi_gemm_bf16_rows(const void* x, const void* w, void* out, int 
     p.res_stride = res_stride;
     p.error = error;
     p.swiglu = epilogue == 1 ? 1 : 0;
+    p.act = epilogue >= 2 ? epilogue - 1 : 0;
     p.k_blocks_total = (K + TILE_K - 1) / TILE_K;
     p.k_blocks_per_split = p.k_blocks_total;
     p.swap = 0;

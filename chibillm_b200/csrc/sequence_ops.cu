@@ -268,17 +268,6 @@ __global__ void add_row_vector_kernel(float* __restrict__ acc, long long stride,
     }
 }
 
-// 0: gelu with erf, 1: gelu with tanh, 2: silu, 3: relu
-__device__ __forceinline__ float activate(float z, int kind)
-{
-    switch (kind) {
-    case 0: return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
-    case 1: return 0.5f * z * (1.f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
-    case 2: return z / (1.f + expf(-z));
-    default: return fmaxf(z, 0.f);
-    }
-}
-
 template <typename TX>
 __global__ void activation_kernel(TX* __restrict__ x, long long total, int kind)
 {

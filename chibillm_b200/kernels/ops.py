@@ -288,9 +288,11 @@ class CudaKernels:
             self.scratch_generation += 1
         return buf
 
-    def _linear_of_scaled(self, x: ScaledRows, w: torch.Tensor, out: torch.Tensor, swiglu: bool) -> bool:
-        """out = (the factor of each row) * (x.tensor @ w^T), with SwiGLU if asked,
-        from the kernel for many rows; False if it does not take the shapes."""
+    def _linear_of_scaled(self, x: ScaledRows, w: torch.Tensor, out: torch.Tensor, swiglu: bool,
+                          activation: Optional[str] = None) -> bool:
+        """out = (the factor of each row) * (x.tensor @ w^T), with SwiGLU or an
+        activation if asked, from the kernel for many rows; False if it does not take
+        the shapes."""
         t = x.tensor
         M, K = t.shape
         N = w.shape[0]
@@ -304,7 +306,8 @@ class CudaKernels:
         scale = library.RowScale(_ptr(x.ssq), x.parts, float(x.eps), x.n)
         status = self.lib.chibi_gemm_bf16_rows(
             _ptr(t), _ptr(w), _ptr(out), BF16, None, M, N, K, t.stride(0), w.stride(0), out.stride(0), 0,
-            1 if swiglu else 0, ctypes.byref(scale), None, None, _ptr(self.error), self._stream())
+            1 if swiglu else (2 + self.ACTIVATIONS[activation] if activation is not None else 0),
+            ctypes.byref(scale), None, None, _ptr(self.error), self._stream())
         if status == -2:
             return False
         _check(status, "linear (rows with a factor)")
@@ -1055,13 +1058,31 @@ class CudaKernels:
 
     def linear_activation(self, x, w: torch.Tensor, out: torch.Tensor, kind: str) -> bool:
         """out = act(x @ w^T) with the activation applied to the 32-bit sums: by the
-        kernel that adds up a split product (few rows).  False if this product is not
-        one that is split; nothing has run then."""
+        kernel that adds up a split product (few rows) or in the product's epilogue
+        (many rows; x may be ScaledRows).  False if neither takes the shapes;
+        nothing has run then."""
         if kind not in self.ACTIVATIONS:
             raise KernelError(f"linear_activation: one of {sorted(self.ACTIVATIONS)}")
+        if isinstance(x, ScaledRows):
+            return self._linear_of_scaled(x, w, out, swiglu=False, activation=kind)
         pending = self.linear_partial(x, w)
         if pending is None:
-            return False
+            # many rows: the activation is the product's epilogue
+            M, K = x.shape
+            N = w.shape[0]
+            if not (self.use_tensor_cores and M > 64 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                    and out.dtype == torch.bfloat16 and w.shape[1] == K and out.shape == (M, N)
+                    and x.is_cuda and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1):
+                return False
+            status = self.lib.chibi_gemm_bf16_fused(
+                _ptr(x), _ptr(w), _ptr(out), BF16, None, M, N, K, x.stride(0), w.stride(0), out.stride(0), 0,
+                2 + self.ACTIVATIONS[kind], _ptr(self.error), self._stream())
+            if status == -2:
+                return False
+            _check(status, "linear_activation")
+            self.launches += 1
+            self.tensor_core_calls += 1
+            return True
         if not out.is_contiguous() or out.shape != (pending.M, pending.N):
             raise KernelError("linear_activation: out must be contiguous [M, N]")
         self.launches += 1
