@@ -64,6 +64,13 @@ struct AttnTcParams {
     int window;
     int skip_single;
     int* error;
+    // Options of the score (the kernel with one query tile per CTA only): a soft cap c replaces a
+    // scaled score s by c * tanh(s / c); a bias by distance then takes r1 * ln(1 + r2 * (pos - key))
+    // off, with r1 and r2 per query head.
+    float scale;                   // the plain scale
+    float softcap;                 // 0: none
+    const float* bias_r1;          // [nq] or null
+    const float* bias_r2;
     // The kernel with one query tile per CTA may cut the keys of a row tile into kv_splits ranges,
     // one CTA each (few query rows over a long context would leave most SMs idle otherwise): every
     // CTA then leaves its unnormalised output, maximum and sum per row, and
@@ -298,6 +305,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const int pos = live ? pos0 + tok : -1;
         const int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        // with options the scores are brought to their final form (in units of log2) right after
+        // they are read, and the scale below is 1
+        const bool options = p.softcap > 0.f || p.bias_r1 != nullptr;
+        const float sl2 = options ? 1.f : p.scale_log2;
+        const int bias_head = kv_head * p.group + (live ? r - tok * p.group : 0);
+        const float r1 = p.bias_r1 ? p.bias_r1[bias_head] : 0.f, r2 = p.bias_r1 ? p.bias_r2[bias_head] : 0.f;
+        const float two_over_cap_log2 = p.softcap > 0.f ? 2.f * 1.4426950408889634f / p.softcap : 0.f;
         // The output accumulates in TMEM over all tiles.  `m` is the maximum that the exponents are
         // taken against; it follows the true maximum only when that has grown by more than 2^8
         // (then the output so far is rescaled in TMEM, a rare event after the first tiles), so
@@ -317,6 +331,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             tmem_load_wait();
             tcgen05_fence_before();
             mbar_arrive(&s_free[st]);                        // the MMA thread may fill this buffer again
+            if (options) {
+#pragma unroll
+                for (int i = 0; i < KEYS; ++i) {
+                    float v = __uint_as_float(sv[i]) * p.scale;
+                    if (p.softcap > 0.f)                     // c * tanh(v / c) = c * (1 - 2 / (exp(2 v / c) + 1))
+                        v = p.softcap * (1.f - __fdividef(2.f, fast_exp2(v * two_over_cap_log2) + 1.f));
+                    const int dist = pos - (key0 + i);
+                    v -= r1 * __logf(1.f + r2 * (float)(dist > 0 ? dist : 0));
+                    sv[i] = __float_as_uint(v * 1.4426950408889634f);
+                }
+            }
             // masks only where a row's visible range ends inside the tile; the warp takes one path
             const bool masked = __any_sync(0xffffffffu, key0 + KEYS - 1 > pos || key0 < first);
             if (masked) {
@@ -335,7 +360,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     mx4[u] = fmaxf(mx4[u], __uint_as_float(sv[i + u]));
             }
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            mx *= p.scale_log2;                              // the scale is positive
+            mx *= sl2;                                       // the scale is positive
             const bool grow = mx > m + 8.f;                  // also true for the first visible key (m = -inf)
             if (__any_sync(0xffffffffu, grow && m != -INFINITY && j > 0)) {
                 // rescale what has accumulated: the product of tile j-1 must have landed first
@@ -369,8 +394,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 uint32_t packed[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(sv[8 * c + 2 * i]), p.scale_log2, -base));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(sv[8 * c + 2 * i + 1]), p.scale_log2, -base));
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(sv[8 * c + 2 * i]), sl2, -base));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(sv[8 * c + 2 * i + 1]), sl2, -base));
                     sum4[i] += p0 + p1;
                     const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                     packed[i] = *reinterpret_cast<const uint32_t*>(&h);
@@ -885,12 +910,19 @@ CHIBI_API int chibi_attention_prefill_tc(const void* q, const void* k_cache, con
                                          int page_size, int num_pages, float scale, int window,
                                          int skip_single, int max_q_len, int variant, int kv_splits,
                                          float* scratch, long long scratch_floats, long long tokens,
+                                         float softcap, const float* bias_r1, const float* bias_r2,
                                          int* error, cudaStream_t stream)
 {
     if (seqs <= 0)
         return CHIBI_OK;
-    if (nkv <= 0 || nq % nkv != 0 || window < 0 || variant < 0 || variant > 2)
+    if (nkv <= 0 || nq % nkv != 0 || window < 0 || variant < 0 || variant > 2 || softcap < 0.f
+        || (bias_r1 != nullptr) != (bias_r2 != nullptr))
         return CHIBI_ERR_ARGUMENT;
+    if (softcap > 0.f || bias_r1) {
+        if (variant == 2)
+            return CHIBI_ERR_UNSUPPORTED;
+        variant = 1;                   // the kernel with one query tile per CTA has the options
+    }
     if (page_size < 8 || page_size > 128 || KEYS % page_size != 0
         || (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15)
         || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
@@ -914,6 +946,10 @@ CHIBI_API int chibi_attention_prefill_tc(const void* q, const void* k_cache, con
     p.skip_single = skip_single;
     p.error = error;
     p.kv_splits = 1;
+    p.scale = scale;
+    p.softcap = softcap;
+    p.bias_r1 = bias_r1;
+    p.bias_r2 = bias_r2;
     CUtensorMap mk, mv;
     if (!tensor_map_2d(k_cache, p.cache_rows, D, D, page_size, &mk)
         || !tensor_map_2d(v_cache, p.cache_rows, D, D, page_size, &mv))

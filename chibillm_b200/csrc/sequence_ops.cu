@@ -70,7 +70,7 @@ constexpr int DELTA_THREADS = DELTA_LANES * DELTA_COLS;
 struct DeltaParams {
     const void* proj;                 // [T, stride]: r | k | v | gate | removal | low, heads * d each but low
     long long stride;
-    const float* decay_out;           // [heads * d, rank]
+    const float* decay_out;           // [rank, heads * d]: transposed, so that a warp's channels lie side by side
     const float* decay_bias;          // [heads * d]
     const float* removal_bias;        // [heads * d]
     float* state;                     // [slots, heads, d (value), d (key)]
@@ -78,6 +78,7 @@ struct DeltaParams {
     const int* q_start;
     const int* slots;
     int heads, d, rank, chunk;
+    int late_trigger;                 // several chunks: the kernel after this one is let in only at the end
     float decay_scale, key_eps;
 };
 
@@ -89,10 +90,21 @@ __device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-
 // five vectors of each token (decay, rate * unit key, unit key, key, receptance; a warp
 // per token), then every thread runs the recurrence over the chunk on its part of the
 // state, which stays in registers from the sequence's first token of the step to its last.
+//
+// A sequence of many tokens keeps its CTAs busy for milliseconds.  The kernel that follows must not
+// be let in at the start, as the short kernels do it: its CTAs would sit on the SMs waiting and
+// take issue slots from the recurrence (a prompt of 2,048 tokens took 38 ms instead of 6).  With
+// several chunks the kernel therefore triggers its dependents after the last token.
 template <int R, typename TX>
 __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(const DeltaParams p)
 {
+#ifdef CHIBI_TIMELINE
     pdl_enter();
+#else
+    if (!p.late_trigger)
+        pdl_trigger();
+    pdl_wait();
+#endif
     extern __shared__ __align__(16) float smem[];
     constexpr int DP = R * DELTA_LANES;                     // padded head size
     const int d = p.d, W = p.heads * d;
@@ -140,10 +152,10 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(const DeltaPa
                 float decay = 0.f, au = 0.f, u = 0.f, k = 0.f, r = 0.f;
                 if (c < d) {
                     const int f = head * d + c;
-                    const float* wrow = p.decay_out + (size_t)f * p.rank;
+                    const float* wcol = p.decay_out + f;
                     float z = 0.f;
                     for (int j = 0; j < p.rank; ++j)
-                        z = fmaf(wrow[j], low[j], z);
+                        z = fmaf(wcol[(size_t)j * W], low[j], z);
                     decay = expf(-p.decay_scale * sigmoidf_(z + p.decay_bias[f]));
                     k = to_f32(row[W + f]);
                     r = to_f32(row[f]);
@@ -198,6 +210,10 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(const DeltaPa
                 p.o[(size_t)(row0 + base + tt) * W + head * d + col] = acc;
         }
     }
+#ifndef CHIBI_TIMELINE
+    if (p.late_trigger)
+        pdl_trigger();
+#endif
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         const int row = part * R + i;
@@ -335,6 +351,7 @@ static int launch_delta(const DeltaParams& p, int seqs, int max_q_len, cudaStrea
     chunk = chunk > max_q_len ? max_q_len : chunk;
     DeltaParams q = p;
     q.chunk = chunk;
+    q.late_trigger = max_q_len > chunk ? 1 : 0;
     const dim3 grid((unsigned)((p.d + DELTA_COLS - 1) / DELTA_COLS), (unsigned)p.heads, (unsigned)seqs);
     launch(delta_rule_kernel<R, TX>, grid, dim3(DELTA_THREADS), (size_t)chunk * per_token * sizeof(float), stream, q);
     return launch_status();
@@ -352,7 +369,7 @@ CHIBI_API int chibi_delta_rule(const void* proj, int x_type, long long stride, c
     if (d > 256 || heads > 65535 || seqs > 65535)
         return CHIBI_ERR_UNSUPPORTED;
     DeltaParams p = { proj, stride, decay_out, decay_bias, removal_bias, state, o, q_start, slots,
-                      heads, d, rank, 0, decay_scale, key_eps };
+                      heads, d, rank, 0, 0, decay_scale, key_eps };
     const int rows = (d + DELTA_LANES - 1) / DELTA_LANES;
     CHIBI_DISPATCH_TYPE(x_type, TX, {
         if (rows <= 4)

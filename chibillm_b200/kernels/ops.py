@@ -839,8 +839,8 @@ class CudaKernels:
             lib = self._attention_libs[d] = self._profiled(lib)
         seqs = ctx_len.numel()
         mode = 1 if max_q_len == 1 else (2 if min_q_len > 1 else 3)
-        plain_scores = softcap == 0.0 and bias_r1 is None and k_cache.data_ptr() != v_cache.data_ptr()
-        if mode & 2 and plain_scores and self.use_tcgen05_attention and d in build.TCGEN05_ATTENTION_HEAD_DIMS \
+        options = softcap != 0.0 or bias_r1 is not None
+        if mode & 2 and self.use_tcgen05_attention and d in build.TCGEN05_ATTENTION_HEAD_DIMS \
                 and page_size >= 8 and 128 % page_size == 0:
             # prompt portions on tcgen05; one-token sequences stay with the split-key kernel
             tc = self._attention_tc_libs.get(d)
@@ -855,8 +855,9 @@ class CudaKernels:
                 _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
                 _ptr(seq_rows), _ptr(q_start), _ptr(ctx_len), seqs, nq, nkv, page_size, k_cache.shape[0],
                 float(scale), int(window or 0), 1 if mode & 1 else 0, int(max_q_len),
-                int(self.tcgen05_attention_variant), kv_splits, _ptr(part),
-                part.numel() if part is not None else 0, q.shape[0], _ptr(self.error), self._stream())
+                1 if options else int(self.tcgen05_attention_variant), kv_splits, _ptr(part),
+                part.numel() if part is not None else 0, q.shape[0], float(softcap), _ptr(bias_r1), _ptr(bias_r2),
+                _ptr(self.error), self._stream())
             if status == 0:
                 # (key ranges belong to the kernel with one query tile per CTA, and bring a merge kernel)
                 self.launches += 2 if kv_splits > 1 and self.tcgen05_attention_variant != 2 else 1
@@ -979,7 +980,8 @@ class CudaKernels:
                    max_q_len: int) -> None:
         """The generalised delta rule over the step's tokens of every sequence.
         ``proj`` [T, 5 * heads * d + rank] holds r | k | v | gate | removal | low.  Per
-        head: w = exp(-decay_scale * sigmoid(decay_out tanh(low) + decay_bias)),
+        head: w = exp(-decay_scale * sigmoid(decay_out^T tanh(low) + decay_bias)) with
+        ``decay_out`` [rank, heads * d] (the stored matrix transposed),
         a = sigmoid(removal + removal_bias), u = k / sqrt(sum(k^2) + key_eps);
         S <- diag(w) S - (a u)(u^T S) + k v^T; o = S^T r.  ``state`` [slots, heads, d, d]
         float32 holds S with the value index before the key index."""
@@ -987,7 +989,7 @@ class CudaKernels:
         _rows_contiguous(proj, "delta_rule: proj")
         T = proj.shape[0]
         W = heads * d
-        for t, shape, what in ((decay_out, (W, rank), "decay_out"), (decay_bias, (W,), "decay_bias"),
+        for t, shape, what in ((decay_out, (rank, W), "decay_out"), (decay_bias, (W,), "decay_bias"),
                                (removal_bias, (W,), "removal_bias"), (o, (T, W), "o")):
             if t.dtype != torch.float32 or tuple(t.shape) != shape or not t.is_contiguous():
                 raise KernelError(f"delta_rule: {what} must be contiguous float32 {shape}")

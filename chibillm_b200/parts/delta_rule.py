@@ -31,7 +31,7 @@ class DeltaRuleMixer(Mixer):
         self.names = names
         self.runtime = runtime
         self.stacked: torch.Tensor = None        # r | k | v | gate | removal | decay_in
-        self.decay_out: torch.Tensor = None      # [heads * d, rank] 32-bit
+        self.decay_out: torch.Tensor = None      # [rank, heads * d] 32-bit: transposed for the kernel
         self.decay_bias: torch.Tensor = None
         self.removal_bias: torch.Tensor = None
         self.norm_weight: torch.Tensor = None
@@ -52,7 +52,7 @@ class DeltaRuleMixer(Mixer):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         mats = [tensors[self.names[r]] for r in _PROJECTIONS] + [tensors[self.names["decay_in"]]]
         self.stacked = torch.cat([m.to(mats[0].dtype) for m in mats], dim=0).contiguous()
-        self.decay_out = tensors[self.names["decay_out"]].float().contiguous()
+        self.decay_out = tensors[self.names["decay_out"]].float().t().contiguous()
         self.decay_bias = tensors[self.names["decay_bias"]].float().contiguous()
         self.removal_bias = tensors[self.names["removal_bias"]].float().contiguous()
         self.norm_weight = tensors[self.names["out_norm"]].float().contiguous()

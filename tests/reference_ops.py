@@ -176,13 +176,14 @@ class ReferenceKernels:
 
     def delta_rule(self, proj, decay_out, decay_bias, removal_bias, state, o, q_start, state_slots, heads, d,
                    rank, decay_scale, key_eps, max_q_len):
-        """proj [T, 5 * heads * d + rank] = r | k | v | gate | removal | low; state
-        [slots, heads, d, d] (key rows, value columns); o [T, heads * d] 32-bit."""
+        """proj [T, 5 * heads * d + rank] = r | k | v | gate | removal | low; decay_out
+        [rank, heads * d]; state [slots, heads, d, d] (value index first); o [T, heads * d]
+        32-bit."""
         self._count("delta_rule")
         W = heads * d
         p = proj.float()
         low = torch.tanh(p[:, 5 * W:5 * W + rank])
-        decay = torch.exp(-decay_scale * torch.sigmoid(low @ decay_out.float().t() + decay_bias.float()))
+        decay = torch.exp(-decay_scale * torch.sigmoid(low @ decay_out.float() + decay_bias.float()))
         rate = torch.sigmoid(p[:, 4 * W:5 * W] + removal_bias.float())
         for s in range(state_slots.numel()):
             slot = int(state_slots[s])
@@ -191,9 +192,9 @@ class ReferenceKernels:
                     c = slice(h * d, (h + 1) * d)
                     r, k, v = p[t, c], p[t, W + h * d:W + (h + 1) * d], p[t, 2 * W + h * d:2 * W + (h + 1) * d]
                     u = k / torch.sqrt((k * k).sum() + key_eps)
-                    S = state[slot, h]
+                    S = state[slot, h].t()
                     S = decay[t, c][:, None] * S - torch.outer(rate[t, c] * u, u @ S) + torch.outer(k, v)
-                    state[slot, h] = S
+                    state[slot, h] = S.t()
                     o[t, c] = S.t() @ r
 
     def gated_group_norm(self, x, gate, weight, eps, group, out):

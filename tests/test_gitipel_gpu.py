@@ -125,7 +125,7 @@ def test_delta_rule_kernel(kernels, dtype, heads, d, rank):
             q_start = torch.tensor(np.cumsum([0] + [b - a for _, a, b in step]), dtype=torch.int32, device=DEV)
             slot_t = torch.tensor([slots[s] for s, _, _ in step], dtype=torch.int32, device=DEV)
             o = torch.empty(proj.shape[0], W, dtype=torch.float32, device=DEV)
-            kernels.delta_rule(proj, w2.to(DEV), w0.to(DEV), ab.to(DEV), state, o, q_start, slot_t, heads, d, rank,
+            kernels.delta_rule(proj, w2.t().contiguous().to(DEV), w0.to(DEV), ab.to(DEV), state, o, q_start, slot_t, heads, d, rank,
                                scale, eps, max(b - a for _, a, b in step))
             at = 0
             for s, a, b in step:
@@ -157,7 +157,7 @@ def test_delta_rule_forgets_and_removes(kernels):
         state = torch.zeros(1, 1, d, d, device=DEV)
         o = torch.empty(T, W, device=DEV)
         q_start = torch.tensor([0, T], dtype=torch.int32, device=DEV)
-        kernels.delta_rule(proj.to(DEV), w2.to(DEV), w0.to(DEV), ab.to(DEV), state, o, q_start,
+        kernels.delta_rule(proj.to(DEV), w2.t().contiguous().to(DEV), w0.to(DEV), ab.to(DEV), state, o, q_start,
                            torch.zeros(1, dtype=torch.int32, device=DEV), 1, d, 1, math.exp(-0.5), 1e-6, T)
         ref, _ = delta_reference(proj, w2, w0, ab, 1, d, 1, math.exp(-0.5), 1e-6)
         close(o[:T - 1], ref[:T - 1, 0], 1e-5, "delta rule, the tokens before the last")
