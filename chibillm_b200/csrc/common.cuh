@@ -31,13 +31,14 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
     return __float2bfloat16_rn(v);
 }
 
-// Activations by code, in 32-bit: 0 gelu with erf, 1 gelu with tanh, 2 silu, 3 relu.
+// Activations by code, in 32-bit: 0 gelu with erf, 1 gelu with tanh, 2 silu, 3 relu, 4 tanh.
 __device__ __forceinline__ float activate(float z, int kind)
 {
     switch (kind) {
     case 0: return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
     case 1: return 0.5f * z * (1.f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
     case 2: return z / (1.f + expf(-z));
+    case 4: return tanhf(z);
     default: return fmaxf(z, 0.f);
     }
 }

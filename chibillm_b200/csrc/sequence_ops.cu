@@ -71,6 +71,8 @@ struct DeltaParams {
     const void* proj;                 // [T, stride]: r | k | v | gate | removal | low, heads * d each but low
     long long stride;
     const float* decay_out;           // [rank, heads * d]: transposed, so that a warp's channels lie side by side
+    const float* decay_logits;        // [T, heads * d] = tanh(low) decay_out, made by a matrix product before
+                                      // this kernel (many tokens), or null: the kernel adds them up itself
     const float* decay_bias;          // [heads * d]
     const float* removal_bias;        // [heads * d]
     float* state;                     // [slots, heads, d (value), d (key)]
@@ -138,8 +140,9 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(const DeltaPa
             float* v5 = smem + (size_t)tt * per_token;
             float* low = v5 + 5 * DP + DELTA_COLS;
             const TX* row = proj + (size_t)(row0 + base + tt) * p.stride;
-            for (int j = lane; j < p.rank; j += 32)
-                low[j] = tanhf(to_f32(row[5 * (size_t)W + j]));
+            if (!p.decay_logits)
+                for (int j = lane; j < p.rank; j += 32)
+                    low[j] = tanhf(to_f32(row[5 * (size_t)W + j]));
             float ksq = 0.f;
             for (int c = lane; c < d; c += 32) {
                 const float k = to_f32(row[W + head * d + c]);
@@ -152,10 +155,15 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(const DeltaPa
                 float decay = 0.f, au = 0.f, u = 0.f, k = 0.f, r = 0.f;
                 if (c < d) {
                     const int f = head * d + c;
-                    const float* wcol = p.decay_out + f;
                     float z = 0.f;
-                    for (int j = 0; j < p.rank; ++j)
-                        z = fmaf(wcol[(size_t)j * W], low[j], z);
+                    if (p.decay_logits) {
+                        z = p.decay_logits[(size_t)(row0 + base + tt) * W + f];
+                    } else {
+                        const float* wcol = p.decay_out + f;
+#pragma unroll 8
+                        for (int j = 0; j < p.rank; ++j)
+                            z = fmaf(wcol[(size_t)j * W], low[j], z);
+                    }
                     decay = expf(-p.decay_scale * sigmoidf_(z + p.decay_bias[f]));
                     k = to_f32(row[W + f]);
                     r = to_f32(row[f]);
@@ -259,7 +267,7 @@ __global__ void scale_kernel(float* __restrict__ x, float factor, long long tota
 
 template <typename TX, typename TO>
 __global__ void cast_rows_kernel(const TX* __restrict__ x, long long x_stride, TO* __restrict__ out,
-                                 long long out_stride, long long rows, int n)
+                                 long long out_stride, long long rows, int n, int act)
 {
     pdl_enter();
     const long long total = rows * n;
@@ -267,7 +275,8 @@ __global__ void cast_rows_kernel(const TX* __restrict__ x, long long x_stride, T
          i += (long long)gridDim.x * blockDim.x) {
         const long long r = i / n;
         const int c = (int)(i - r * n);
-        out[(size_t)r * out_stride + c] = from_f32<TO>(to_f32(x[(size_t)r * x_stride + c]));
+        const float v = to_f32(x[(size_t)r * x_stride + c]);
+        out[(size_t)r * out_stride + c] = from_f32<TO>(act >= 0 ? activate(v, act) : v);
     }
 }
 
@@ -358,17 +367,17 @@ static int launch_delta(const DeltaParams& p, int seqs, int max_q_len, cudaStrea
 }
 
 CHIBI_API int chibi_delta_rule(const void* proj, int x_type, long long stride, const float* decay_out,
-                               const float* decay_bias, const float* removal_bias, float* state, float* o,
+                               const float* decay_logits, const float* decay_bias, const float* removal_bias, float* state, float* o,
                                const int* q_start, const int* slots, int seqs, int max_q_len, int heads, int d,
                                int rank, float decay_scale, float key_eps, cudaStream_t stream)
 {
     if (seqs <= 0 || max_q_len <= 0)
         return CHIBI_OK;
-    if (heads <= 0 || d <= 0 || rank <= 0)
+    if (heads <= 0 || d <= 0 || rank <= 0 || (!decay_out && !decay_logits))
         return CHIBI_ERR_ARGUMENT;
     if (d > 256 || heads > 65535 || seqs > 65535)
         return CHIBI_ERR_UNSUPPORTED;
-    DeltaParams p = { proj, stride, decay_out, decay_bias, removal_bias, state, o, q_start, slots,
+    DeltaParams p = { proj, stride, decay_out, decay_logits, decay_bias, removal_bias, state, o, q_start, slots,
                       heads, d, rank, 0, 0, decay_scale, key_eps };
     const int rows = (d + DELTA_LANES - 1) / DELTA_LANES;
     CHIBI_DISPATCH_TYPE(x_type, TX, {
@@ -414,14 +423,17 @@ CHIBI_API int chibi_scale(float* x, float factor, long long total, cudaStream_t 
     return launch_status();
 }
 
+// `act`: -1 none, else the activation by that code is applied on the way.
 CHIBI_API int chibi_cast_rows(const void* x, int x_type, long long x_stride, void* out, int out_type,
-                              long long out_stride, long long rows, int n, cudaStream_t stream)
+                              long long out_stride, long long rows, int n, int act, cudaStream_t stream)
 {
     if (rows <= 0 || n <= 0)
         return CHIBI_OK;
+    if (act < -1 || act > 4)
+        return CHIBI_ERR_ARGUMENT;
     CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(out_type, TO, {
         launch(cast_rows_kernel<TX, TO>, dim3(blocks_for(rows * n, 256)), dim3(256), 0, stream, (const TX*)x, x_stride,
-               (TO*)out, out_stride, rows, n);
+               (TO*)out, out_stride, rows, n, act);
     }));
     return launch_status();
 }
@@ -439,7 +451,7 @@ CHIBI_API int chibi_activation(void* x, int x_type, long long total, int kind, c
 {
     if (total <= 0)
         return CHIBI_OK;
-    if (kind < 0 || kind > 3)
+    if (kind < 0 || kind > 4)
         return CHIBI_ERR_ARGUMENT;
     CHIBI_DISPATCH_TYPE(x_type, TX, {
         launch(activation_kernel<TX>, dim3(blocks_for(total, 256)), dim3(256), 0, stream, (TX*)x, total, kind);
@@ -452,7 +464,7 @@ CHIBI_API int chibi_reduce_activation(const float* partial, int splits, long lon
 {
     if (total <= 0)
         return CHIBI_OK;
-    if (kind < 0 || kind > 3 || splits < 1)
+    if (kind < 0 || kind > 4 || splits < 1)
         return CHIBI_ERR_ARGUMENT;
     CHIBI_DISPATCH_TYPE(out_type, TO, {
         launch(reduce_activation_kernel<TO>, dim3(blocks_for(total, 256)), dim3(256), 0, stream, partial, splits, total,

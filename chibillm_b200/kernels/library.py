@@ -47,10 +47,10 @@ _SIGNATURES = {
                                               I, I, F, F, I, P, P],
         "chibi_attention_generic": [P, I, P, P, I, P, P, I, P, P, P, P, P, L, I, I, I, I, I, F, I, F, P, P, P, P],
         "chibi_short_conv": [P, I, L, P, P, P, L, P, P, I, I, I, I, P],
-        "chibi_delta_rule": [P, I, L, P, P, P, P, P, P, P, I, I, I, I, I, F, F, P],
+        "chibi_delta_rule": [P, I, L, P, P, P, P, P, P, P, P, I, I, I, I, I, F, F, P],
         "chibi_gated_group_norm": [P, P, I, L, P, P, I, L, I, I, F, P],
         "chibi_scale": [P, F, L, P],
-        "chibi_cast_rows": [P, I, L, P, I, L, L, I, P],
+        "chibi_cast_rows": [P, I, L, P, I, L, L, I, I, P],
         "chibi_add_row_vector": [P, L, P, L, I, P],
         "chibi_activation": [P, I, L, I, P],
         "chibi_reduce_activation": [P, I, L, P, I, I, P],

@@ -306,7 +306,7 @@ class CudaKernels:
         scale = library.RowScale(_ptr(x.ssq), x.parts, float(x.eps), x.n)
         status = self.lib.chibi_gemm_bf16_rows(
             _ptr(t), _ptr(w), _ptr(out), BF16, None, M, N, K, t.stride(0), w.stride(0), out.stride(0), 0,
-            1 if swiglu else (2 + self.ACTIVATIONS[activation] if activation is not None else 0),
+            1 if swiglu else (2 + self._EPILOGUE_ACTIVATIONS[activation] if activation is not None else 0),
             ctypes.byref(scale), None, None, _ptr(self.error), self._stream())
         if status == -2:
             return False
@@ -977,15 +977,20 @@ class CudaKernels:
     def delta_rule(self, proj: torch.Tensor, decay_out: torch.Tensor, decay_bias: torch.Tensor,
                    removal_bias: torch.Tensor, state: torch.Tensor, o: torch.Tensor, q_start: torch.Tensor,
                    state_slots: torch.Tensor, heads: int, d: int, rank: int, decay_scale: float, key_eps: float,
-                   max_q_len: int) -> None:
+                   max_q_len: int, decay_logits: Optional[torch.Tensor] = None) -> None:
         """The generalised delta rule over the step's tokens of every sequence.
         ``proj`` [T, 5 * heads * d + rank] holds r | k | v | gate | removal | low.  Per
         head: w = exp(-decay_scale * sigmoid(decay_out^T tanh(low) + decay_bias)) with
         ``decay_out`` [rank, heads * d] (the stored matrix transposed),
         a = sigmoid(removal + removal_bias), u = k / sqrt(sum(k^2) + key_eps);
         S <- diag(w) S - (a u)(u^T S) + k v^T; o = S^T r.  ``state`` [slots, heads, d, d]
-        float32 holds S with the value index before the key index."""
-        _need_cuda(proj, decay_out, decay_bias, removal_bias, state, o, q_start, state_slots)
+        float32 holds S with the value index before the key index.  ``decay_logits``
+        float32 [T, heads * d], if given, is tanh(low) decay_out made beforehand (a matrix
+        product, for many tokens); the kernel then adds up nothing itself."""
+        _need_cuda(proj, decay_out, decay_bias, removal_bias, state, o, q_start, state_slots, decay_logits)
+        if decay_logits is not None and (decay_logits.dtype != torch.float32 or not decay_logits.is_contiguous()
+                                         or decay_logits.shape != (proj.shape[0], heads * d)):
+            raise KernelError("delta_rule: decay_logits must be contiguous float32 [T, heads * d]")
         _rows_contiguous(proj, "delta_rule: proj")
         T = proj.shape[0]
         W = heads * d
@@ -997,7 +1002,8 @@ class CudaKernels:
                 or tuple(state.shape[1:]) != (heads, d, d):
             raise KernelError("delta_rule: proj [T, 5 * heads * d + rank] and state float32 [slots, heads, d, d]")
         self.launches += 1
-        _check(self.lib.chibi_delta_rule(_ptr(proj), _code(proj), proj.stride(0), _ptr(decay_out), _ptr(decay_bias),
+        _check(self.lib.chibi_delta_rule(_ptr(proj), _code(proj), proj.stride(0), _ptr(decay_out), _ptr(decay_logits),
+                                         _ptr(decay_bias),
                                          _ptr(removal_bias), _ptr(state), _ptr(o), _ptr(q_start), _ptr(state_slots),
                                          state_slots.numel(), int(max_q_len), heads, d, rank, float(decay_scale),
                                          float(key_eps), self._stream()), "delta_rule")
@@ -1025,16 +1031,20 @@ class CudaKernels:
         self.launches += 1
         _check(self.lib.chibi_scale(_ptr(x), float(factor), x.numel(), self._stream()), "scale")
 
-    def cast_rows(self, x: torch.Tensor, out: torch.Tensor) -> None:
-        """out = x in out's type; both [rows, n], rows may be strided."""
+    def cast_rows(self, x: torch.Tensor, out: torch.Tensor, activation: Optional[str] = None) -> None:
+        """out = x (or act(x)) in out's type; both [rows, n], rows may be strided."""
         _need_cuda(x, out)
         _rows_contiguous(x, "cast_rows: x")
         _rows_contiguous(out, "cast_rows: out")
         if x.shape != out.shape:
             raise KernelError("cast_rows: shapes")
         self.launches += 1
+        if activation is not None and activation not in self.ACTIVATIONS:
+            raise KernelError(f"cast_rows: activation must be one of {sorted(self.ACTIVATIONS)}")
         _check(self.lib.chibi_cast_rows(_ptr(x), _code(x), x.stride(0), _ptr(out), _code(out), out.stride(0),
-                                        x.shape[0], x.shape[1], self._stream()), "cast_rows")
+                                        x.shape[0], x.shape[1],
+                                        self.ACTIVATIONS[activation] if activation is not None else -1,
+                                        self._stream()), "cast_rows")
 
     def add_row_vector(self, acc: torch.Tensor, vec: torch.Tensor) -> None:
         """acc[r, :] += vec for every row (both float32)."""
@@ -1047,7 +1057,9 @@ class CudaKernels:
         _check(self.lib.chibi_add_row_vector(_ptr(acc), acc.stride(0), _ptr(vec), acc.shape[0], acc.shape[1],
                                              self._stream()), "add_row_vector")
 
-    ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+    ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "tanh": 4}
+
+    _EPILOGUE_ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}    # what a product's epilogue takes
 
     def activation(self, x: torch.Tensor, kind: str) -> None:
         """x = act(x) in place, computed in 32-bit."""
@@ -1066,19 +1078,21 @@ class CudaKernels:
         if kind not in self.ACTIVATIONS:
             raise KernelError(f"linear_activation: one of {sorted(self.ACTIVATIONS)}")
         if isinstance(x, ScaledRows):
-            return self._linear_of_scaled(x, w, out, swiglu=False, activation=kind)
+            return kind in self._EPILOGUE_ACTIVATIONS and self._linear_of_scaled(x, w, out, swiglu=False,
+                                                                                  activation=kind)
         pending = self.linear_partial(x, w)
         if pending is None:
             # many rows: the activation is the product's epilogue
             M, K = x.shape
             N = w.shape[0]
-            if not (self.use_tensor_cores and M > 64 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            if not (self.use_tensor_cores and M > 64 and kind in self._EPILOGUE_ACTIVATIONS
+                    and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
                     and out.dtype == torch.bfloat16 and w.shape[1] == K and out.shape == (M, N)
                     and x.is_cuda and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1):
                 return False
             status = self.lib.chibi_gemm_bf16_fused(
                 _ptr(x), _ptr(w), _ptr(out), BF16, None, M, N, K, x.stride(0), w.stride(0), out.stride(0), 0,
-                2 + self.ACTIVATIONS[kind], _ptr(self.error), self._stream())
+                2 + self._EPILOGUE_ACTIVATIONS[kind], _ptr(self.error), self._stream())
             if status == -2:
                 return False
             _check(status, "linear_activation")

@@ -32,6 +32,7 @@ class DeltaRuleMixer(Mixer):
         self.runtime = runtime
         self.stacked: torch.Tensor = None        # r | k | v | gate | removal | decay_in
         self.decay_out: torch.Tensor = None      # [rank, heads * d] 32-bit: transposed for the kernel
+        self.decay_out_matrix: torch.Tensor = None
         self.decay_bias: torch.Tensor = None
         self.removal_bias: torch.Tensor = None
         self.norm_weight: torch.Tensor = None
@@ -53,12 +54,14 @@ class DeltaRuleMixer(Mixer):
         mats = [tensors[self.names[r]] for r in _PROJECTIONS] + [tensors[self.names["decay_in"]]]
         self.stacked = torch.cat([m.to(mats[0].dtype) for m in mats], dim=0).contiguous()
         self.decay_out = tensors[self.names["decay_out"]].float().t().contiguous()
+        self.decay_out_matrix = tensors[self.names["decay_out"]].contiguous()      # [heads * d, rank] for a product
         self.decay_bias = tensors[self.names["decay_bias"]].float().contiguous()
         self.removal_bias = tensors[self.names["removal_bias"]].float().contiguous()
         self.norm_weight = tensors[self.names["out_norm"]].float().contiguous()
         self.o_proj = tensors[self.names["o_proj"]].contiguous()
 
     accepts_scaled_rows = True       # x goes to the stacked product and nowhere else
+    LOGITS_BY_PRODUCT_FROM = 32      # steps of more tokens make the decay's logits with a matrix product
 
     def cache_need(self):
         s = self.spec
@@ -75,9 +78,17 @@ class DeltaRuleMixer(Mixer):
         proj = ctx.workspace.get("delta.proj", (T, self.stacked.shape[0]), rt.dtype)
         k.linear(x, self.stacked, proj)
         o = ctx.workspace.get("delta.o", (T, width), torch.float32)
+        logits = None
+        if T > self.LOGITS_BY_PRODUCT_FROM:
+            # many tokens: tanh(low) W2^T is a matrix product of its own (the recurrence would add up
+            # rank terms per token and channel, one token after the other)
+            low = ctx.workspace.get("delta.low", (T, s.decay_rank), rt.dtype)
+            k.cast_rows(proj[:, 5 * width:], low, activation="tanh")
+            logits = ctx.workspace.get("delta.decay_logits", (T, width), torch.float32)
+            k.linear(low, self.decay_out_matrix, logits)
         k.delta_rule(proj, self.decay_out, self.decay_bias, self.removal_bias, cache.arrays["state"], o,
                      ctx.q_start, ctx.state_slots, s.num_heads, s.head_dim, s.decay_rank, s.decay_scale,
-                     s.key_eps, ctx.max_q_len)
+                     s.key_eps, ctx.max_q_len, decay_logits=logits)
         gated = ctx.workspace.get("delta.gated", (T, width), rt.dtype)
         k.gated_group_norm(o, proj[:, 3 * width:4 * width], self.norm_weight, s.norm_eps, s.head_dim, gated)
         return k.linear(gated, self.o_proj, residual, residual=residual, defer=True)

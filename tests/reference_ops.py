@@ -134,8 +134,10 @@ class ReferenceKernels:
         self._count("scale")
         x.mul_(factor)
 
-    def cast_rows(self, x, out):
+    def cast_rows(self, x, out, activation=None):
         out.copy_(x.to(out.dtype))
+        if activation is not None:
+            self.activation(out, activation)
 
     def add_row_vector(self, acc, vec):
         acc.add_(vec.float()[None, :])
@@ -151,6 +153,8 @@ class ReferenceKernels:
             y = z / (1.0 + torch.exp(-z))
         elif kind == "relu":
             y = torch.clamp(z, min=0.0)
+        elif kind == "tanh":
+            y = torch.tanh(z)
         else:
             raise ValueError(kind)
         x.copy_(y.to(x.dtype))
@@ -175,7 +179,7 @@ class ReferenceKernels:
                 history[slot, :keep] = seq[seq.shape[0] - keep:].to(history.dtype)
 
     def delta_rule(self, proj, decay_out, decay_bias, removal_bias, state, o, q_start, state_slots, heads, d,
-                   rank, decay_scale, key_eps, max_q_len):
+                   rank, decay_scale, key_eps, max_q_len, decay_logits=None):
         """proj [T, 5 * heads * d + rank] = r | k | v | gate | removal | low; decay_out
         [rank, heads * d]; state [slots, heads, d, d] (value index first); o [T, heads * d]
         32-bit."""
@@ -183,7 +187,8 @@ class ReferenceKernels:
         W = heads * d
         p = proj.float()
         low = torch.tanh(p[:, 5 * W:5 * W + rank])
-        decay = torch.exp(-decay_scale * torch.sigmoid(low @ decay_out.float() + decay_bias.float()))
+        logits = low @ decay_out.float() if decay_logits is None else decay_logits.float()
+        decay = torch.exp(-decay_scale * torch.sigmoid(logits + decay_bias.float()))
         rate = torch.sigmoid(p[:, 4 * W:5 * W] + removal_bias.float())
         for s in range(state_slots.numel()):
             slot = int(state_slots[s])

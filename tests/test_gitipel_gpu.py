@@ -117,7 +117,8 @@ def test_delta_rule_kernel(kernels, dtype, heads, d, rank):
     scale, eps = math.exp(-0.5), 1e-6
     refs = [delta_reference(p, w2, w0, ab, heads, d, rank, scale, eps) for p in projs]
     state = torch.full((3, heads, d, d), float("nan"), dtype=torch.float32, device=DEV)
-    for sizes in ([64], [1, 2, 5, 17]):
+    # the third round hands the kernel the decay's logits ready made (what a step of many tokens does)
+    for sizes, ready in (([64], False), ([1, 2, 5, 17], False), ([64], True)):
         state[:] = 0
         got = [torch.zeros(n, W) for n in lengths]
         for step in batches_of(lengths, sizes, seed=rank):
@@ -125,8 +126,9 @@ def test_delta_rule_kernel(kernels, dtype, heads, d, rank):
             q_start = torch.tensor(np.cumsum([0] + [b - a for _, a, b in step]), dtype=torch.int32, device=DEV)
             slot_t = torch.tensor([slots[s] for s, _, _ in step], dtype=torch.int32, device=DEV)
             o = torch.empty(proj.shape[0], W, dtype=torch.float32, device=DEV)
+            logits = (torch.tanh(proj[:, 5 * W:].double().cpu()) @ w2.double().t()).float().to(DEV) if ready else None
             kernels.delta_rule(proj, w2.t().contiguous().to(DEV), w0.to(DEV), ab.to(DEV), state, o, q_start, slot_t, heads, d, rank,
-                               scale, eps, max(b - a for _, a, b in step))
+                               scale, eps, max(b - a for _, a, b in step), decay_logits=logits)
             at = 0
             for s, a, b in step:
                 got[s][a:b] = o[at:at + b - a].cpu()

@@ -192,3 +192,32 @@ def test_random_model_folder_of_the_package(tmp_path):
     with safe_open(os.path.join(folder, "model.safetensors"), framework="pt") as f:
         assert (f.get_tensor("l0.mix.r2") > 0).all()          # the logarithm's argument stays positive
         assert tuple(f.get_tensor("l1.mix.w1").shape) == (6, cfg["width"])
+
+
+def test_command_line_and_scheduler_on_cpu(tmp_path):
+    """Four prompts through the package's command line with room for three at a
+    time and portions of 8 tokens: the scheduler mixes portions with decoded
+    tokens, a request waits for a slot, and every greedy token is the plain
+    implementation's best one (wherever that leads by more than rounding)."""
+    import io
+    from chibillm_b200 import cli
+    cfg = gitipel_models.get("G1")
+    folder = gitipel_models.write_model(cfg, str(tmp_path / "g1"), seed=4)
+    prompts = list(helpers.random_requests(cfg["vocab"], [1, 7, 23, 30], seed=1).values())
+    argv = ["--context-length", "64", "--max-tokens", "5", "--max-seqs", "3", "--max-batch-tokens", "16",
+            "--prefill-chunk", "8", "--dtype", "float32", "--ignore-eos", "--no-stream"]
+    for p in prompts:
+        argv += ["--prompt-ids", ",".join(map(str, p))]
+    out, err = io.StringIO(), io.StringIO()
+    assert cli.run(cli.parse_cli_options(argv + [folder]), io.StringIO(""), out, err,
+                   kernels=ReferenceKernels(), device="cpu") == 0, err.getvalue()
+    replies = [[int(t) for t in line.split()] for line in out.getvalue().splitlines()]
+    assert len(replies) == 4 and all(len(r) == 5 for r in replies)
+    assert err.getvalue().count("[stop] len_limit") == 4
+    for prompt, new in zip(prompts, replies):
+        ref = gitipel_models.plain_logits(cfg, 4, {"a": prompt + new})["a"]
+        for i, tok in enumerate(new):
+            row = ref[len(prompt) + i - 1]
+            top = torch.topk(row, 2).values
+            if float(top[0] - top[1]) > 1e-4 * float(row.abs().max()):
+                assert int(torch.argmax(row)) == tok
