@@ -43,6 +43,23 @@ __device__ __forceinline__ float activate(float z, int kind)
     }
 }
 
+// The same for sums that become bfloat16 at once (a product's epilogue): the exact gelu with
+// erfc(x) = t (a1 + t (a2 + t (a3 + t (a4 + t a5)))) exp(-x^2), t = 1 / (1 + p x), x >= 0, which
+// is good to 1.5e-7 (a thousand times finer than the output's rounding) and costs two
+// special-function operations instead of erff's branches; the tail of negative arguments keeps its
+// relative accuracy because erfc is used there without a difference.
+__device__ __forceinline__ float activate_rounded(float z, int kind)
+{
+    if (kind != 0)
+        return activate(z, kind);
+    const float x = fabsf(z) * 0.70710678118654752f;
+    const float t = __fdividef(1.f, fmaf(0.3275911f, x, 1.f));
+    const float poly = t * fmaf(t, fmaf(t, fmaf(t, fmaf(t, 1.061405429f, -1.453152027f), 1.421413741f), -0.284496736f),
+                                0.254829592f);
+    const float erfc_x = poly * __expf(-x * x);
+    return 0.5f * z * (z < 0.f ? erfc_x : 2.f - erfc_x);
+}
+
 __device__ __forceinline__ float warp_sum(float v)
 {
 #pragma unroll

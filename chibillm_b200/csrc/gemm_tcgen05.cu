@@ -542,8 +542,8 @@ __device__ __noinline__ void epilogue_rows_activated(const GemmParams& p, uint32
                 __nv_bfloat162 v[4];
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
-                    v[q] = __floats2bfloat162_rn(activate(inv * __uint_as_float(r32[8 * j + 2 * q]), kind),
-                                                 activate(inv * __uint_as_float(r32[8 * j + 2 * q + 1]), kind));
+                    v[q] = __floats2bfloat162_rn(activate_rounded(inv * __uint_as_float(r32[8 * j + 2 * q]), kind),
+                                                 activate_rounded(inv * __uint_as_float(r32[8 * j + 2 * q + 1]), kind));
                 *stage_unit(stage, lane, 4 * h + j) = *reinterpret_cast<uint4*>(v);
             }
         }
