@@ -521,45 +521,9 @@ __device__ __forceinline__ void epilogue_heads(const GemmParams& p, uint32_t tad
     }
 }
 
-// The bfloat16 output with an activation on the sums (factor of the row first).  Kept out of
-// line: the products without an activation keep their registers.
-template <int BN>
-__device__ __noinline__ void epilogue_rows_activated(const GemmParams& p, uint32_t taddr, int m0, int lane,
-                                                     int tile_b, uint8_t* stage, float inv)
-{
-    const int sub = lane >> 3, unit = lane & 7;
-    const int kind = p.act - 1;
-    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
-#pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 64) {
-#pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-            uint32_t r32[32];
-            tmem_load_32x32(taddr + c0 + 32 * h, r32);
-            tmem_load_wait();
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                __nv_bfloat162 v[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    v[q] = __floats2bfloat162_rn(activate_rounded(inv * __uint_as_float(r32[8 * j + 2 * q]), kind),
-                                                 activate_rounded(inv * __uint_as_float(r32[8 * j + 2 * q + 1]), kind));
-                *stage_unit(stage, lane, 4 * h + j) = *reinterpret_cast<uint4*>(v);
-            }
-        }
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int r = 4 * i + sub;
-            const uint4 v = *stage_unit(stage, r, unit);
-            if (m0 + r < p.M)
-                *reinterpret_cast<uint4*>(out + (size_t)(m0 + r) * p.out_stride + tile_b * BN + c0 + unit * 8) = v;
-        }
-        __syncwarp();
-    }
-}
-
-template <int BN>
+// ACT: the instantiation for products with an activation on their sums (GemmParams::act).  It is a
+// kernel of its own, so that the products without one keep their registers.
+template <int BN, bool ACT = false>
 __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_t taddr, int m0, int lane,
                                                     int tile_b, uint8_t* stage, const float* head_w = nullptr)
 {
@@ -722,10 +686,6 @@ __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_
         }
         return;
     }
-    if (p.act && p.out_type == CHIBI_BF16 && !p.residual && inside && p.out_stride % 8 == 0) {
-        epilogue_rows_activated<BN>(p, taddr, m0, lane, tile_b, stage, inv);
-        return;
-    }
     if (p.out_type == CHIBI_BF16 && !p.residual && inside && p.out_stride % 8 == 0) {
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
 #pragma unroll 1
@@ -739,9 +699,14 @@ __device__ __forceinline__ void epilogue_token_rows(const GemmParams& p, uint32_
                 for (int j = 0; j < 4; ++j) {
                     __nv_bfloat162 v[4];
 #pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        v[q] = __floats2bfloat162_rn(inv * __uint_as_float(r32[8 * j + 2 * q]),
-                                                     inv * __uint_as_float(r32[8 * j + 2 * q + 1]));
+                    for (int q = 0; q < 4; ++q) {
+                        float lo = inv * __uint_as_float(r32[8 * j + 2 * q]), hi = inv * __uint_as_float(r32[8 * j + 2 * q + 1]);
+                        if constexpr (ACT) {
+                            lo = activate_rounded(lo, p.act - 1);
+                            hi = activate_rounded(hi, p.act - 1);
+                        }
+                        v[q] = __floats2bfloat162_rn(lo, hi);
+                    }
                     *stage_unit(stage, lane, 4 * h + j) = *reinterpret_cast<uint4*>(v);
                 }
             }
@@ -965,7 +930,7 @@ __device__ __forceinline__ void tile_of(int t, int tiles_m, int tiles_total, int
 // x is the A operand (many rows).  One CTA per SM walks over the output tiles (tile_of above).
 // Two accumulators in TMEM: while the four epilogue warps read one tile out, the MMA thread
 // already fills the other.
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool ACT = false>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                                const __grid_constant__ CUtensorMap map_b, const GemmParams p,
@@ -1099,7 +1064,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                 }
             }
             if (!piece)
-                epilogue_token_rows<BN>(p, taddr, tile_a * TILE_A + quarter * 32, lane, tile_b,
+                epilogue_token_rows<BN, ACT>(p, taddr, tile_a * TILE_A + quarter * 32, lane, tile_b,
                                         stage_base + quarter * EPILOGUE_STAGE_BYTES, head_w);
             tcgen05_fence_before();
             mbar_arrive(&tmem_empty_bar[buf]);
@@ -1127,7 +1092,7 @@ struct PairSmem {
     static constexpr int B_BYTES = (BN / 2) * TILE_K * 2;       // this CTA's half of the tile's rows of w
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 };
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool ACT = false>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                          const GemmParams p, int tiles_m, int tiles_total)
@@ -1247,7 +1212,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 break;
             tcgen05_fence_after();
             const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-            epilogue_token_rows<BN>(p, taddr, (tile_a * 2 + (int)rank) * TILE_A + quarter * 32, lane, tile_b,
+            epilogue_token_rows<BN, ACT>(p, taddr, (tile_a * 2 + (int)rank) * TILE_A + quarter * 32, lane, tile_b,
                                     stage_base + quarter * EPILOGUE_STAGE_BYTES, head_w);
             tcgen05_fence_before();
             mbar_arrive_cluster(peer_smem_addr(smem_addr(&tmem_empty_bar[buf]), 0));     // the even CTA's
@@ -1306,15 +1271,21 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
     return launch_status();
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool ACT = false>
 static int launch_gemm_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p,
                                   int tiles_m, int tiles_n, cudaStream_t stream, bool share_last_round = true)
 {
+    if constexpr (!ACT) {
+        // an activation in the staged bfloat16 epilogue: the kernel instantiated for it
+        if (p.act && p.out_type == CHIBI_BF16 && !p.residual && p.N % BN == 0 && p.out_stride % 8 == 0
+            && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0)
+            return launch_gemm_persistent<BN, STAGES, true>(ma, mb, p, tiles_m, tiles_n, stream, share_last_round);
+    }
     constexpr size_t smem = STAGES * GemmSmem<BN>::STAGE_BYTES + (2 * STAGES + 4 + 12) * 8 + 16
         + 4 * EPILOGUE_STAGE_BYTES + 2 * 128 * sizeof(float) + 1024;
     static bool configured = false;
     if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BN, STAGES>,
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BN, STAGES, ACT>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess)
             return (int)e;
@@ -1359,22 +1330,27 @@ static int launch_gemm_persistent(const CUtensorMap& ma, const CUtensorMap& mb, 
             }
         }
     }
-    launch(gemm_tcgen05_persistent_kernel<BN, STAGES>, dim3(ctas), dim3(GEMM_THREADS), smem, stream, ma, mb, q,
+    launch(gemm_tcgen05_persistent_kernel<BN, STAGES, ACT>, dim3(ctas), dim3(GEMM_THREADS), smem, stream, ma, mb, q,
            tiles_m, tiles);
     return launch_status();
 }
 
 // Pairs of CTAs on tiles of 256 rows x BN columns (gemm_tcgen05_pair_kernel); tiles_m counts blocks of 256 rows.
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool ACT = false>
 static int launch_gemm_pairs(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int tiles_m,
                              int tiles_n, cudaStream_t stream)
 {
+    if constexpr (!ACT) {
+        if (p.act && p.out_type == CHIBI_BF16 && !p.residual && p.N % BN == 0 && p.out_stride % 8 == 0
+            && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0)
+            return launch_gemm_pairs<BN, STAGES, true>(ma, mb, p, tiles_m, tiles_n, stream);
+    }
     constexpr size_t smem = STAGES * PairSmem<BN>::STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 4 * EPILOGUE_STAGE_BYTES
         + 2 * 128 * sizeof(float) + 1024;
     static_assert(smem <= 227 * 1024, "the stages must fit the shared memory of an SM");
     static bool configured = false;
     if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<BN, STAGES>,
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<BN, STAGES, ACT>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess)
             return (int)e;
@@ -1398,7 +1374,7 @@ static int launch_gemm_pairs(const CUtensorMap& ma, const CUtensorMap& mb, const
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_pair_kernel<BN, STAGES>, &cfg) != cudaSuccess
+        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_pair_kernel<BN, STAGES, ACT>, &cfg) != cudaSuccess
             || clusters < 1) {
             cudaGetLastError();
             clusters = sms / 2;
@@ -1406,7 +1382,7 @@ static int launch_gemm_pairs(const CUtensorMap& ma, const CUtensorMap& mb, const
         resident_pairs = clusters < sms / 2 ? clusters : sms / 2;
     }
     const int pairs = tiles < resident_pairs ? tiles : resident_pairs;
-    launch_cluster_x(gemm_tcgen05_pair_kernel<BN, STAGES>, dim3(2 * pairs), dim3(GEMM_THREADS), smem, stream, 2, ma,
+    launch_cluster_x(gemm_tcgen05_pair_kernel<BN, STAGES, ACT>, dim3(2 * pairs), dim3(GEMM_THREADS), smem, stream, 2, ma,
                      mb, p, tiles_m, tiles);
     return launch_status();
 }

@@ -64,8 +64,10 @@ short_conv_kernel(const TX* __restrict__ x, long long x_stride, const float* __r
 
 // ---------------------------------------------------------------- delta rule
 constexpr int DELTA_LANES = 8;        // threads that share a value column (its key rows in equal parts)
-constexpr int DELTA_COLS = 16;        // value columns per CTA
-constexpr int DELTA_THREADS = DELTA_LANES * DELTA_COLS;
+constexpr int DELTA_WARPS = 4;        // warps that run the recurrence
+constexpr int DELTA_PRODUCERS = 8;    // warps that make the next chunk's vectors meanwhile
+constexpr int DELTA_THREADS = (DELTA_WARPS + DELTA_PRODUCERS) * 32;
+constexpr int DELTA_CHUNK = 16;       // most tokens whose vectors are in shared memory at a time
 
 struct DeltaParams {
     const void* proj;                 // [T, stride]: r | k | v | gate | removal | low, heads * d each but low
@@ -86,18 +88,25 @@ struct DeltaParams {
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
 
-// grid (column blocks, heads, sequences).  R: key rows per thread (a thread owns rows
-// lane * R .. lane * R + R - 1 of its column; rows beyond d are zeros).  The sequence's
-// tokens are taken in chunks: first all threads turn the chunk's projections into the
-// five vectors of each token (decay, rate * unit key, unit key, key, receptance; a warp
-// per token), then every thread runs the recurrence over the chunk on its part of the
-// state, which stays in registers from the sequence's first token of the step to its last.
+// grid (column blocks, heads, sequences), four warps.  A thread owns R key rows (rows
+// part * R .. part * R + R - 1; rows beyond d are zeros) of CPT neighbouring value columns; the
+// eight threads of a column group sit side by side in a warp, a warp holds four groups, a CTA
+// 16 * CPT columns.  Several columns to a thread, because every thread reads the same five
+// vectors of a token from shared memory: with one column each, those reads (20 KB a token and
+// CTA) bound the kernel.  The sequence's tokens are taken in chunks, and the warps have two
+// roles.  Eight producer warps turn a chunk's projections into the five vectors of each token
+// (decay, rate * unit key, unit key, key, receptance) in one of two buffers in shared memory,
+// several tokens to a warp with their loads in flight together; meanwhile the four warps of the
+// recurrence walk over the chunk before, each thread on its part of the state, which stays in
+// registers from the sequence's first token of the step to its last.  One block barrier a chunk.
+// (Alone, the vectors of 2,048 tokens of 16 heads take 0.77 ms and the recurrence 0.60 ms; one
+// after the other they took 1.35 ms.)
 //
 // A sequence of many tokens keeps its CTAs busy for milliseconds.  The kernel that follows must not
 // be let in at the start, as the short kernels do it: its CTAs would sit on the SMs waiting and
 // take issue slots from the recurrence (a prompt of 2,048 tokens took 38 ms instead of 6).  With
 // several chunks the kernel therefore triggers its dependents after the last token.
-template <int R, typename TX>
+template <int R, int CPT, typename TX>
 __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(const DeltaParams p)
 {
 #ifdef CHIBI_TIMELINE
@@ -109,124 +118,225 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(const DeltaPa
 #endif
     extern __shared__ __align__(16) float smem[];
     constexpr int DP = R * DELTA_LANES;                     // padded head size
+    constexpr int COLS = 16 * CPT;                          // value columns of this CTA
+    constexpr int TPW = DELTA_CHUNK / DELTA_PRODUCERS;      // tokens a producer warp prepares per chunk
     const int d = p.d, W = p.heads * d;
     const int head = blockIdx.y, seq = blockIdx.z;
-    const int col0 = blockIdx.x * DELTA_COLS;
     const int row0 = p.q_start[seq];
     const int q_len = p.q_start[seq + 1] - row0;
     if (q_len <= 0)
         return;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int cc = threadIdx.x / DELTA_LANES, part = threadIdx.x % DELTA_LANES;
-    const int col = col0 + cc;
-    const bool col_ok = col < d;
-    // shared: per token of the chunk [decay | rate * u | u | k | r] (DP each), then v (DELTA_COLS),
-    // then tanh(low) (rank)
-    const int per_token = 5 * DP + DELTA_COLS + ((p.rank + 3) & ~3);      // a multiple of four floats
+    const bool producer = threadIdx.x >= DELTA_WARPS * 32;
+    const int warp = producer ? (threadIdx.x >> 5) - DELTA_WARPS : threadIdx.x >> 5;     // the index within the role
+    const int lane = threadIdx.x & 31;
+    const int part = lane & (DELTA_LANES - 1);
+    const int cta_col0 = blockIdx.x * COLS;
+    const int my_col0 = cta_col0 + (warp * 4 + (lane >> 3)) * CPT;       // this thread's first column
+    // shared: per token of the chunk [decay | rate * u | u | k | r] (DP each), then v (COLS),
+    // then tanh(low) (rank, padded to a multiple of four floats)
+    const int per_token = 5 * DP + COLS + ((p.rank + 3) & ~3);
     const TX* proj = static_cast<const TX*>(p.proj);
 
-    float S[R];
-    float* st = p.state + (((size_t)p.slots[seq] * p.heads + head) * d + (col_ok ? col : 0)) * d;
+    float S[CPT][R];
+    float* st = p.state + ((size_t)p.slots[seq] * p.heads + head) * d * d;
+    if (!producer) {
 #pragma unroll
-    for (int i = 0; i < R; ++i) {
-        const int row = part * R + i;
-        S[i] = (col_ok && row < d) ? st[row] : 0.f;
+        for (int j = 0; j < CPT; ++j)
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                const int row = part * R + i, col = my_col0 + j;
+                S[j][i] = (col < d && row < d) ? st[(size_t)col * d + row] : 0.f;
+            }
     }
+    float* const buffers = smem;
+    const int buffer_floats = p.chunk * per_token;
 
-    for (int base = 0; base < q_len; base += p.chunk) {
-        const int n = min(p.chunk, q_len - base);
-        __syncthreads();                                    // the chunk before has been used up
-        for (int tt = warp; tt < n; tt += DELTA_THREADS / 32) {
-            float* v5 = smem + (size_t)tt * per_token;
-            float* low = v5 + 5 * DP + DELTA_COLS;
-            const TX* row = proj + (size_t)(row0 + base + tt) * p.stride;
-            if (!p.decay_logits)
-                for (int j = lane; j < p.rank; j += 32)
-                    low[j] = tanhf(to_f32(row[5 * (size_t)W + j]));
-            float ksq = 0.f;
-            for (int c = lane; c < d; c += 32) {
-                const float k = to_f32(row[W + head * d + c]);
-                ksq = fmaf(k, k, ksq);
-            }
-            ksq = warp_sum(ksq);
-            __syncwarp();
-            const float inv = 1.f / sqrtf(ksq + p.key_eps);
-            for (int c = lane; c < DP; c += 32) {
-                float decay = 0.f, au = 0.f, u = 0.f, k = 0.f, r = 0.f;
-                if (c < d) {
-                    const int f = head * d + c;
-                    float z = 0.f;
-                    if (p.decay_logits) {
-                        z = p.decay_logits[(size_t)(row0 + base + tt) * W + f];
-                    } else {
-                        const float* wcol = p.decay_out + f;
-#pragma unroll 8
-                        for (int j = 0; j < p.rank; ++j)
-                            z = fmaf(wcol[(size_t)j * W], low[j], z);
-                    }
-                    decay = expf(-p.decay_scale * sigmoidf_(z + p.decay_bias[f]));
-                    k = to_f32(row[W + f]);
-                    r = to_f32(row[f]);
-                    u = k * inv;
-                    au = sigmoidf_(to_f32(row[4 * (size_t)W + f]) + p.removal_bias[f]) * u;
-                }
-                v5[c] = decay;
-                v5[DP + c] = au;
-                v5[2 * DP + c] = u;
-                v5[3 * DP + c] = k;
-                v5[4 * DP + c] = r;
-            }
-            if (lane < DELTA_COLS)
-                v5[5 * DP + lane] = col0 + lane < d ? to_f32(row[2 * (size_t)W + head * d + col0 + lane]) : 0.f;
-        }
-        __syncthreads();
-        for (int tt = 0; tt < n; ++tt) {
-            const float* v5 = smem + (size_t)tt * per_token + part * R;
-            const float v = smem[(size_t)tt * per_token + 5 * DP + cc];
-            float dot = 0.f;
+    // turn c = -1: the producers fill buffer 0 with chunk 0; turn c >= 0: they fill the other buffer
+    // with chunk c + 1 while the recurrence walks over chunk c
+    const int chunks = (q_len + p.chunk - 1) / p.chunk;
+    for (int c = -1; c < chunks; ++c) {
+        if (producer) {
+        const int base = (c + 1) * p.chunk;
+        const int n = min(p.chunk, q_len - base);           // <= 0 after the last chunk
+        float* const smem = buffers + ((c + 1) & 1) * buffer_floats;
+        if (n > 0) {
+        // ---- the chunk's vectors: producer warp w takes tokens w, w + 4, ...
+        float inv[TPW];
 #pragma unroll
-            for (int i = 0; i < R; i += 4) {
-                const float4 u = *reinterpret_cast<const float4*>(v5 + 2 * DP + i);
-                dot = fmaf(u.x, S[i], dot);
-                dot = fmaf(u.y, S[i + 1], dot);
-                dot = fmaf(u.z, S[i + 2], dot);
-                dot = fmaf(u.w, S[i + 3], dot);
+        for (int u = 0; u < TPW; ++u)
+            inv[u] = 0.f;
+        for (int c = lane; c < d; c += 32) {
+            float k[TPW];
+#pragma unroll
+            for (int u = 0; u < TPW; ++u) {
+                const int tt = warp + DELTA_PRODUCERS * u;
+                k[u] = tt < n ? to_f32(proj[(size_t)(row0 + base + tt) * p.stride + W + head * d + c]) : 0.f;
             }
-            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-            float acc = 0.f;
+#pragma unroll
+            for (int u = 0; u < TPW; ++u)
+                inv[u] = fmaf(k[u], k[u], inv[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < TPW; ++u)
+            inv[u] = 1.f / sqrtf(warp_sum(inv[u]) + p.key_eps);
+        if (!p.decay_logits) {
+#pragma unroll
+            for (int u = 0; u < TPW; ++u) {
+                const int tt = warp + DELTA_PRODUCERS * u;
+                if (tt < n) {
+                    float* low = smem + (size_t)tt * per_token + 5 * DP + COLS;
+                    for (int j = lane; j < p.rank; j += 32)
+                        low[j] = tanhf(to_f32(proj[(size_t)(row0 + base + tt) * p.stride + 5 * (size_t)W + j]));
+                }
+            }
+            __syncwarp();
+        }
+        for (int c = lane; c < DP; c += 32) {
+            const int f = head * d + c;
+            float z[TPW], kk[TPW], rr[TPW], aa[TPW];
+#pragma unroll
+            for (int u = 0; u < TPW; ++u) {
+                const int tt = warp + DELTA_PRODUCERS * u;
+                z[u] = kk[u] = rr[u] = aa[u] = 0.f;
+                if (tt < n && c < d) {
+                    const TX* row = proj + (size_t)(row0 + base + tt) * p.stride;
+                    kk[u] = to_f32(row[W + f]);
+                    rr[u] = to_f32(row[f]);
+                    aa[u] = to_f32(row[4 * (size_t)W + f]);
+                    if (p.decay_logits)
+                        z[u] = p.decay_logits[(size_t)(row0 + base + tt) * W + f];
+                }
+            }
+            if (!p.decay_logits && c < d) {
+                const float* wcol = p.decay_out + f;
+                for (int j = 0; j < p.rank; ++j) {
+                    const float wj = wcol[(size_t)j * W];
+#pragma unroll
+                    for (int u = 0; u < TPW; ++u) {
+                        const int tt = warp + DELTA_PRODUCERS * u;
+                        if (tt < n)
+                            z[u] = fmaf(wj, smem[(size_t)tt * per_token + 5 * DP + COLS + j], z[u]);
+                    }
+                }
+            }
+            const float wb = c < d ? p.decay_bias[f] : 0.f, ab = c < d ? p.removal_bias[f] : 0.f;
+#pragma unroll
+            for (int u = 0; u < TPW; ++u) {
+                const int tt = warp + DELTA_PRODUCERS * u;
+                if (tt < n) {
+                    float* v5 = smem + (size_t)tt * per_token;
+                    const float unit = kk[u] * inv[u];
+                    v5[c] = c < d ? expf(-p.decay_scale * sigmoidf_(z[u] + wb)) : 0.f;
+                    v5[DP + c] = c < d ? sigmoidf_(aa[u] + ab) * unit : 0.f;
+                    v5[2 * DP + c] = unit;
+                    v5[3 * DP + c] = kk[u];
+                    v5[4 * DP + c] = rr[u];
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < TPW; ++u) {
+            const int tt = warp + DELTA_PRODUCERS * u;
+            if (tt < n)
+                for (int c = lane; c < COLS; c += 32)
+                    smem[(size_t)tt * per_token + 5 * DP + c] = cta_col0 + c < d
+                        ? to_f32(proj[(size_t)(row0 + base + tt) * p.stride + 2 * (size_t)W + head * d + cta_col0 + c]) : 0.f;
+        }
+        }
+        } else if (c >= 0) {
+        const int base = c * p.chunk;
+        const int n = min(p.chunk, q_len - base);
+        const float* const smem = buffers + (c & 1) * buffer_floats;
+        // ---- the recurrence over the chunk.  A token's turn is a chain: u . S over the thread's
+        // rows, three shuffles, the update, S . r, three shuffles.  The state of the next token
+        // needs the first half only, so the sum over the lanes of S . r is put off by one token:
+        // its shuffles are issued beside those of the next token's u . S and wait with them.
+        float acc_prev[CPT];
+        int o_prev = -1;                                    // the token whose S . r is still to be added up
+#pragma unroll
+        for (int j = 0; j < CPT; ++j)
+            acc_prev[j] = 0.f;
+        for (int tt = 0; tt <= n; ++tt) {
+            const bool live = tt < n;
+            const int at = live ? tt : n - 1;
+            const float* v5 = smem + (size_t)at * per_token + part * R;
+            const float* vv = smem + (size_t)at * per_token + 5 * DP + (my_col0 - cta_col0);
+            float dot[CPT], dot2[CPT], acc[CPT], acc2[CPT], v[CPT];
+#pragma unroll
+            for (int j = 0; j < CPT; ++j) {
+                dot[j] = dot2[j] = acc[j] = acc2[j] = 0.f;
+                v[j] = vv[j];
+            }
+            if (live) {
+#pragma unroll
+                for (int i = 0; i < R; i += 4) {
+                    const float4 u = *reinterpret_cast<const float4*>(v5 + 2 * DP + i);
+#pragma unroll
+                    for (int j = 0; j < CPT; ++j) {
+                        dot[j] = fmaf(u.x, S[j][i], fmaf(u.y, S[j][i + 1], dot[j]));
+                        dot2[j] = fmaf(u.z, S[j][i + 2], fmaf(u.w, S[j][i + 3], dot2[j]));
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < CPT; ++j)
+                dot[j] += dot2[j];
+#pragma unroll
+            for (int step = 1; step < DELTA_LANES; step <<= 1) {
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) {
+                    const float a = __shfl_xor_sync(0xffffffffu, dot[j], step);
+                    const float b = __shfl_xor_sync(0xffffffffu, acc_prev[j], step);
+                    dot[j] += a;
+                    acc_prev[j] += b;
+                }
+            }
+            if (o_prev >= 0 && part == 0) {
+                float* dst = p.o + (size_t)(row0 + base + o_prev) * W + head * d + my_col0;
+#pragma unroll
+                for (int j = 0; j < CPT; ++j)
+                    if (my_col0 + j < d)
+                        dst[j] = acc_prev[j];
+            }
+            if (!live)
+                break;
 #pragma unroll
             for (int i = 0; i < R; i += 4) {
                 const float4 w = *reinterpret_cast<const float4*>(v5 + i);
                 const float4 au = *reinterpret_cast<const float4*>(v5 + DP + i);
                 const float4 k = *reinterpret_cast<const float4*>(v5 + 3 * DP + i);
                 const float4 r = *reinterpret_cast<const float4*>(v5 + 4 * DP + i);
-                S[i] = fmaf(k.x, v, fmaf(w.x, S[i], -au.x * dot));
-                S[i + 1] = fmaf(k.y, v, fmaf(w.y, S[i + 1], -au.y * dot));
-                S[i + 2] = fmaf(k.z, v, fmaf(w.z, S[i + 2], -au.z * dot));
-                S[i + 3] = fmaf(k.w, v, fmaf(w.w, S[i + 3], -au.w * dot));
-                acc = fmaf(S[i], r.x, acc);
-                acc = fmaf(S[i + 1], r.y, acc);
-                acc = fmaf(S[i + 2], r.z, acc);
-                acc = fmaf(S[i + 3], r.w, acc);
+#pragma unroll
+                for (int j = 0; j < CPT; ++j) {
+                    S[j][i] = fmaf(k.x, v[j], fmaf(w.x, S[j][i], -au.x * dot[j]));
+                    S[j][i + 1] = fmaf(k.y, v[j], fmaf(w.y, S[j][i + 1], -au.y * dot[j]));
+                    S[j][i + 2] = fmaf(k.z, v[j], fmaf(w.z, S[j][i + 2], -au.z * dot[j]));
+                    S[j][i + 3] = fmaf(k.w, v[j], fmaf(w.w, S[j][i + 3], -au.w * dot[j]));
+                    acc[j] = fmaf(S[j][i], r.x, fmaf(S[j][i + 1], r.y, acc[j]));
+                    acc2[j] = fmaf(S[j][i + 2], r.z, fmaf(S[j][i + 3], r.w, acc2[j]));
+                }
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            if (part == 0 && col_ok)
-                p.o[(size_t)(row0 + base + tt) * W + head * d + col] = acc;
+#pragma unroll
+            for (int j = 0; j < CPT; ++j)
+                acc_prev[j] = acc[j] + acc2[j];
+            o_prev = tt;
         }
+        }
+        __syncthreads();                                    // the next chunk's vectors are there, this chunk's buffer is free
     }
 #ifndef CHIBI_TIMELINE
     if (p.late_trigger)
         pdl_trigger();
 #endif
+    if (!producer) {
 #pragma unroll
-    for (int i = 0; i < R; ++i) {
-        const int row = part * R + i;
-        if (col_ok && row < d)
-            st[row] = S[i];
+        for (int j = 0; j < CPT; ++j)
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                const int row = part * R + i, col = my_col0 + j;
+                if (col < d && row < d)
+                    st[(size_t)col * d + row] = S[j][i];
+            }
     }
 }
 
@@ -348,28 +458,40 @@ CHIBI_API int chibi_short_conv(const void* x, int x_type, long long x_stride, co
     return launch_status();
 }
 
-template <int R, typename TX>
+template <int R, int CPT, typename TX>
 static int launch_delta(const DeltaParams& p, int seqs, int max_q_len, cudaStream_t stream)
 {
     constexpr int DP = R * DELTA_LANES;
-    const int per_token = 5 * DP + DELTA_COLS + ((p.rank + 3) & ~3);
-    int chunk = (int)((46 * 1024) / (per_token * sizeof(float)));
+    constexpr int COLS = 16 * CPT;
+    const int per_token = 5 * DP + COLS + ((p.rank + 3) & ~3);
+    // two buffers of `chunk` tokens each, within 96 KB a CTA (two CTAs to an SM)
+    int chunk = (int)((96 * 1024) / (2 * per_token * sizeof(float)));
     if (chunk < 1)
         return CHIBI_ERR_UNSUPPORTED;
-    chunk = chunk > 16 ? 16 : chunk;
+    chunk = chunk > DELTA_CHUNK ? DELTA_CHUNK : chunk;
     chunk = chunk > max_q_len ? max_q_len : chunk;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<R, CPT, TX>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        if (e != cudaSuccess)
+            return (int)e;
+        configured = true;
+    }
     DeltaParams q = p;
     q.chunk = chunk;
     q.late_trigger = max_q_len > chunk ? 1 : 0;
-    const dim3 grid((unsigned)((p.d + DELTA_COLS - 1) / DELTA_COLS), (unsigned)p.heads, (unsigned)seqs);
-    launch(delta_rule_kernel<R, TX>, grid, dim3(DELTA_THREADS), (size_t)chunk * per_token * sizeof(float), stream, q);
+    const dim3 grid((unsigned)((p.d + COLS - 1) / COLS), (unsigned)p.heads, (unsigned)seqs);
+    launch(delta_rule_kernel<R, CPT, TX>, grid, dim3(DELTA_THREADS), (size_t)2 * chunk * per_token * sizeof(float), stream,
+           q);
     return launch_status();
 }
 
 CHIBI_API int chibi_delta_rule(const void* proj, int x_type, long long stride, const float* decay_out,
-                               const float* decay_logits, const float* decay_bias, const float* removal_bias, float* state, float* o,
-                               const int* q_start, const int* slots, int seqs, int max_q_len, int heads, int d,
-                               int rank, float decay_scale, float key_eps, cudaStream_t stream)
+                               const float* decay_logits, const float* decay_bias, const float* removal_bias,
+                               float* state, float* o, const int* q_start, const int* slots, int seqs,
+                               int max_q_len, int heads, int d, int rank, float decay_scale, float key_eps,
+                               cudaStream_t stream)
 {
     if (seqs <= 0 || max_q_len <= 0)
         return CHIBI_OK;
@@ -380,18 +502,22 @@ CHIBI_API int chibi_delta_rule(const void* proj, int x_type, long long stride, c
     DeltaParams p = { proj, stride, decay_out, decay_logits, decay_bias, removal_bias, state, o, q_start, slots,
                       heads, d, rank, 0, 0, decay_scale, key_eps };
     const int rows = (d + DELTA_LANES - 1) / DELTA_LANES;
+    // Columns per thread: one.  More of them (the five vectors of a token are then read once for
+    // several columns) were measured and lose: a warp then issues 350 instructions a token, one
+    // every 5.6 cycles with nothing beside it on its scheduler, and a token's turn is what bounds
+    // a prompt (2,048 tokens of 16 heads: 1.72 ms with four columns a thread).
     CHIBI_DISPATCH_TYPE(x_type, TX, {
         if (rows <= 4)
-            return launch_delta<4, TX>(p, seqs, max_q_len, stream);
+            return launch_delta<4, 1, TX>(p, seqs, max_q_len, stream);
         if (rows <= 8)
-            return launch_delta<8, TX>(p, seqs, max_q_len, stream);
+            return launch_delta<8, 1, TX>(p, seqs, max_q_len, stream);
         if (rows <= 12)
-            return launch_delta<12, TX>(p, seqs, max_q_len, stream);
+            return launch_delta<12, 1, TX>(p, seqs, max_q_len, stream);
         if (rows <= 16)
-            return launch_delta<16, TX>(p, seqs, max_q_len, stream);
+            return launch_delta<16, 1, TX>(p, seqs, max_q_len, stream);
         if (rows <= 24)
-            return launch_delta<24, TX>(p, seqs, max_q_len, stream);
-        return launch_delta<32, TX>(p, seqs, max_q_len, stream);
+            return launch_delta<24, 1, TX>(p, seqs, max_q_len, stream);
+        return launch_delta<32, 1, TX>(p, seqs, max_q_len, stream);
     });
     return CHIBI_OK;
 }
