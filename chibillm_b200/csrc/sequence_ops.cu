@@ -72,9 +72,8 @@ constexpr int DELTA_CHUNK = 16;       // most tokens whose vectors are in shared
 struct DeltaParams {
     const void* proj;                 // [T, stride]: r | k | v | gate | removal | low, heads * d each but low
     long long stride;
-    const float* decay_out;           // [rank, heads * d]: transposed, so that a warp's channels lie side by side
-    const float* decay_logits;        // [T, heads * d] = tanh(low) decay_out, made by a matrix product before
-                                      // this kernel (many tokens), or null: the kernel adds them up itself
+    const float* decay_logits;        // [T, heads * d] = tanh(low) W2^T, made before this kernel (a matrix product
+                                      // for many tokens, decay_logits_kernel for few)
     const float* decay_bias;          // [heads * d]
     const float* removal_bias;        // [heads * d]
     float* state;                     // [slots, heads, d (value), d (key)]
@@ -132,9 +131,8 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(const DeltaPa
     const int part = lane & (DELTA_LANES - 1);
     const int cta_col0 = blockIdx.x * COLS;
     const int my_col0 = cta_col0 + (warp * 4 + (lane >> 3)) * CPT;       // this thread's first column
-    // shared: per token of the chunk [decay | rate * u | u | k | r] (DP each), then v (COLS),
-    // then tanh(low) (rank, padded to a multiple of four floats)
-    const int per_token = 5 * DP + COLS + ((p.rank + 3) & ~3);
+    // shared: per token of the chunk [decay | rate * u | u | k | r] (DP each), then v (COLS)
+    const int per_token = 5 * DP + COLS;
     const TX* proj = static_cast<const TX*>(p.proj);
 
     float S[CPT][R];
@@ -179,18 +177,6 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(const DeltaPa
 #pragma unroll
         for (int u = 0; u < TPW; ++u)
             inv[u] = 1.f / sqrtf(warp_sum(inv[u]) + p.key_eps);
-        if (!p.decay_logits) {
-#pragma unroll
-            for (int u = 0; u < TPW; ++u) {
-                const int tt = warp + DELTA_PRODUCERS * u;
-                if (tt < n) {
-                    float* low = smem + (size_t)tt * per_token + 5 * DP + COLS;
-                    for (int j = lane; j < p.rank; j += 32)
-                        low[j] = tanhf(to_f32(proj[(size_t)(row0 + base + tt) * p.stride + 5 * (size_t)W + j]));
-                }
-            }
-            __syncwarp();
-        }
         for (int c = lane; c < DP; c += 32) {
             const int f = head * d + c;
             float z[TPW], kk[TPW], rr[TPW], aa[TPW];
@@ -203,20 +189,7 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(const DeltaPa
                     kk[u] = to_f32(row[W + f]);
                     rr[u] = to_f32(row[f]);
                     aa[u] = to_f32(row[4 * (size_t)W + f]);
-                    if (p.decay_logits)
-                        z[u] = p.decay_logits[(size_t)(row0 + base + tt) * W + f];
-                }
-            }
-            if (!p.decay_logits && c < d) {
-                const float* wcol = p.decay_out + f;
-                for (int j = 0; j < p.rank; ++j) {
-                    const float wj = wcol[(size_t)j * W];
-#pragma unroll
-                    for (int u = 0; u < TPW; ++u) {
-                        const int tt = warp + DELTA_PRODUCERS * u;
-                        if (tt < n)
-                            z[u] = fmaf(wj, smem[(size_t)tt * per_token + 5 * DP + COLS + j], z[u]);
-                    }
+                    z[u] = p.decay_logits[(size_t)(row0 + base + tt) * W + f];
                 }
             }
             const float wb = c < d ? p.decay_bias[f] : 0.f, ab = c < d ? p.removal_bias[f] : 0.f;
@@ -338,6 +311,36 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(const DeltaPa
                     st[(size_t)col * d + row] = S[j][i];
             }
     }
+}
+
+// ---------------------------------------------------------------- the decay's logits for few tokens
+// out[t, f] = sum_j tanh(low[t, j]) * w2t[j, f]: grid (blocks of 128 channels, tokens).  For steps of
+// few tokens (one launch; the channels of a warp lie side by side in w2t); many tokens take a
+// matrix product on the tensor cores instead.
+template <typename TX>
+__global__ void __launch_bounds__(128)
+decay_logits_kernel(const TX* __restrict__ low, long long low_stride, const float* __restrict__ w2t,
+                    float* __restrict__ out, int W, int rank)
+{
+    pdl_enter();
+    extern __shared__ float low_s[];
+    const int t = blockIdx.y, f = blockIdx.x * 128 + threadIdx.x;
+    for (int j = threadIdx.x; j < rank; j += 128)
+        low_s[j] = tanhf(to_f32(low[(size_t)t * low_stride + j]));
+    __syncthreads();
+    if (f >= W)
+        return;
+    float z = 0.f;
+    for (int j0 = 0; j0 < rank; j0 += 8) {
+        float w[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            w[q] = j0 + q < rank ? w2t[(size_t)(j0 + q) * W + f] : 0.f;
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+            z = fmaf(w[q], j0 + q < rank ? low_s[j0 + q] : 0.f, z);
+    }
+    out[(size_t)t * W + f] = z;
 }
 
 // ---------------------------------------------------------------- gated group norm
@@ -463,7 +466,7 @@ static int launch_delta(const DeltaParams& p, int seqs, int max_q_len, cudaStrea
 {
     constexpr int DP = R * DELTA_LANES;
     constexpr int COLS = 16 * CPT;
-    const int per_token = 5 * DP + COLS + ((p.rank + 3) & ~3);
+    const int per_token = 5 * DP + COLS;
     // two buffers of `chunk` tokens each, within 96 KB a CTA (two CTAs to an SM)
     int chunk = (int)((96 * 1024) / (2 * per_token * sizeof(float)));
     if (chunk < 1)
@@ -487,7 +490,7 @@ static int launch_delta(const DeltaParams& p, int seqs, int max_q_len, cudaStrea
     return launch_status();
 }
 
-CHIBI_API int chibi_delta_rule(const void* proj, int x_type, long long stride, const float* decay_out,
+CHIBI_API int chibi_delta_rule(const void* proj, int x_type, long long stride,
                                const float* decay_logits, const float* decay_bias, const float* removal_bias,
                                float* state, float* o, const int* q_start, const int* slots, int seqs,
                                int max_q_len, int heads, int d, int rank, float decay_scale, float key_eps,
@@ -495,11 +498,11 @@ CHIBI_API int chibi_delta_rule(const void* proj, int x_type, long long stride, c
 {
     if (seqs <= 0 || max_q_len <= 0)
         return CHIBI_OK;
-    if (heads <= 0 || d <= 0 || rank <= 0 || (!decay_out && !decay_logits))
+    if (heads <= 0 || d <= 0 || rank <= 0 || !decay_logits)
         return CHIBI_ERR_ARGUMENT;
     if (d > 256 || heads > 65535 || seqs > 65535)
         return CHIBI_ERR_UNSUPPORTED;
-    DeltaParams p = { proj, stride, decay_out, decay_logits, decay_bias, removal_bias, state, o, q_start, slots,
+    DeltaParams p = { proj, stride, decay_logits, decay_bias, removal_bias, state, o, q_start, slots,
                       heads, d, rank, 0, 0, decay_scale, key_eps };
     const int rows = (d + DELTA_LANES - 1) / DELTA_LANES;
     // Columns per thread: one.  More of them (the five vectors of a token are then read once for
@@ -520,6 +523,23 @@ CHIBI_API int chibi_delta_rule(const void* proj, int x_type, long long stride, c
         return launch_delta<32, 1, TX>(p, seqs, max_q_len, stream);
     });
     return CHIBI_OK;
+}
+
+CHIBI_API int chibi_decay_logits(const void* low, int x_type, long long low_stride, const float* w2t, float* out,
+                                 long long tokens, int W, int rank, cudaStream_t stream)
+{
+    if (tokens <= 0)
+        return CHIBI_OK;
+    if (W <= 0 || rank <= 0)
+        return CHIBI_ERR_ARGUMENT;
+    if (tokens > 65535)
+        return CHIBI_ERR_UNSUPPORTED;
+    const dim3 grid((unsigned)((W + 127) / 128), (unsigned)tokens);
+    CHIBI_DISPATCH_TYPE(x_type, TX, {
+        launch(decay_logits_kernel<TX>, grid, dim3(128), (size_t)rank * sizeof(float), stream, (const TX*)low, low_stride,
+               w2t, out, W, rank);
+    });
+    return launch_status();
 }
 
 CHIBI_API int chibi_gated_group_norm(const float* x, const void* gate, int gate_type, long long gate_stride,

@@ -47,7 +47,8 @@ _SIGNATURES = {
                                               I, I, F, F, I, P, P],
         "chibi_attention_generic": [P, I, P, P, I, P, P, I, P, P, P, P, P, L, I, I, I, I, I, F, I, F, P, P, P, P],
         "chibi_short_conv": [P, I, L, P, P, P, L, P, P, I, I, I, I, P],
-        "chibi_delta_rule": [P, I, L, P, P, P, P, P, P, P, P, I, I, I, I, I, F, F, P],
+        "chibi_delta_rule": [P, I, L, P, P, P, P, P, P, P, I, I, I, I, I, F, F, P],
+        "chibi_decay_logits": [P, I, L, P, P, L, I, I, P],
         "chibi_gated_group_norm": [P, P, I, L, P, P, I, L, I, I, F, P],
         "chibi_scale": [P, F, L, P],
         "chibi_cast_rows": [P, I, L, P, I, L, L, I, I, P],

@@ -974,27 +974,35 @@ class CudaKernels:
                                          out.stride(0), _ptr(q_start), _ptr(state_slots), state_slots.numel(),
                                          int(max_q_len), D, taps, self._stream()), "short_conv")
 
-    def delta_rule(self, proj: torch.Tensor, decay_out: torch.Tensor, decay_bias: torch.Tensor,
+    def decay_logits(self, low: torch.Tensor, w2t: torch.Tensor, out: torch.Tensor) -> None:
+        """out[t] = tanh(low[t]) @ w2t for steps of few tokens: low [T, rank] (rows may be
+        strided), w2t float32 [rank, W], out float32 [T, W]."""
+        _need_cuda(low, w2t, out)
+        _rows_contiguous(low, "decay_logits: low")
+        T, rank = low.shape
+        if w2t.dtype != torch.float32 or w2t.dim() != 2 or w2t.shape[0] != rank or not w2t.is_contiguous() \
+                or out.dtype != torch.float32 or out.shape != (T, w2t.shape[1]) or not out.is_contiguous():
+            raise KernelError("decay_logits: w2t float32 [rank, W] and out float32 [T, W]")
+        self.launches += 1
+        _check(self.lib.chibi_decay_logits(_ptr(low), _code(low), low.stride(0), _ptr(w2t), _ptr(out), T,
+                                           w2t.shape[1], rank, self._stream()), "decay_logits")
+
+    def delta_rule(self, proj: torch.Tensor, decay_logits: torch.Tensor, decay_bias: torch.Tensor,
                    removal_bias: torch.Tensor, state: torch.Tensor, o: torch.Tensor, q_start: torch.Tensor,
                    state_slots: torch.Tensor, heads: int, d: int, rank: int, decay_scale: float, key_eps: float,
-                   max_q_len: int, decay_logits: Optional[torch.Tensor] = None) -> None:
+                   max_q_len: int) -> None:
         """The generalised delta rule over the step's tokens of every sequence.
-        ``proj`` [T, 5 * heads * d + rank] holds r | k | v | gate | removal | low.  Per
-        head: w = exp(-decay_scale * sigmoid(decay_out^T tanh(low) + decay_bias)) with
-        ``decay_out`` [rank, heads * d] (the stored matrix transposed),
+        ``proj`` [T, 5 * heads * d + rank] holds r | k | v | gate | removal | low;
+        ``decay_logits`` float32 [T, heads * d] holds tanh(low) W2^T.  Per head:
+        w = exp(-decay_scale * sigmoid(decay_logits + decay_bias)),
         a = sigmoid(removal + removal_bias), u = k / sqrt(sum(k^2) + key_eps);
         S <- diag(w) S - (a u)(u^T S) + k v^T; o = S^T r.  ``state`` [slots, heads, d, d]
-        float32 holds S with the value index before the key index.  ``decay_logits``
-        float32 [T, heads * d], if given, is tanh(low) decay_out made beforehand (a matrix
-        product, for many tokens); the kernel then adds up nothing itself."""
-        _need_cuda(proj, decay_out, decay_bias, removal_bias, state, o, q_start, state_slots, decay_logits)
-        if decay_logits is not None and (decay_logits.dtype != torch.float32 or not decay_logits.is_contiguous()
-                                         or decay_logits.shape != (proj.shape[0], heads * d)):
-            raise KernelError("delta_rule: decay_logits must be contiguous float32 [T, heads * d]")
+        float32 holds S with the value index before the key index."""
+        _need_cuda(proj, decay_logits, decay_bias, removal_bias, state, o, q_start, state_slots)
         _rows_contiguous(proj, "delta_rule: proj")
         T = proj.shape[0]
         W = heads * d
-        for t, shape, what in ((decay_out, (rank, W), "decay_out"), (decay_bias, (W,), "decay_bias"),
+        for t, shape, what in ((decay_logits, (T, W), "decay_logits"), (decay_bias, (W,), "decay_bias"),
                                (removal_bias, (W,), "removal_bias"), (o, (T, W), "o")):
             if t.dtype != torch.float32 or tuple(t.shape) != shape or not t.is_contiguous():
                 raise KernelError(f"delta_rule: {what} must be contiguous float32 {shape}")
@@ -1002,11 +1010,10 @@ class CudaKernels:
                 or tuple(state.shape[1:]) != (heads, d, d):
             raise KernelError("delta_rule: proj [T, 5 * heads * d + rank] and state float32 [slots, heads, d, d]")
         self.launches += 1
-        _check(self.lib.chibi_delta_rule(_ptr(proj), _code(proj), proj.stride(0), _ptr(decay_out), _ptr(decay_logits),
-                                         _ptr(decay_bias),
-                                         _ptr(removal_bias), _ptr(state), _ptr(o), _ptr(q_start), _ptr(state_slots),
-                                         state_slots.numel(), int(max_q_len), heads, d, rank, float(decay_scale),
-                                         float(key_eps), self._stream()), "delta_rule")
+        _check(self.lib.chibi_delta_rule(_ptr(proj), _code(proj), proj.stride(0), _ptr(decay_logits),
+                                         _ptr(decay_bias), _ptr(removal_bias), _ptr(state), _ptr(o), _ptr(q_start),
+                                         _ptr(state_slots), state_slots.numel(), int(max_q_len), heads, d, rank,
+                                         float(decay_scale), float(key_eps), self._stream()), "delta_rule")
 
     def gated_group_norm(self, x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, group: int,
                          out: torch.Tensor) -> None:

@@ -2,8 +2,9 @@
 matrix per head instead of a cache of keys.
 
 One product gives r | k | v | gate | removal | low-rank decay input for all
-heads.  The recurrence kernel turns them, per token and head, into the decay
-w = exp(-decay_scale * sigmoid(W2 tanh(low) + w0)), the removal rate
+heads.  The decay's logits W2 tanh(low) are made next (a small kernel for few
+tokens, a matrix product for many).  The recurrence kernel turns all of it, per
+token and head, into the decay w = exp(-decay_scale * sigmoid(logits + w0)), the removal rate
 a = sigmoid(removal + bias) and the unit key u = k / sqrt(sum(k^2) + key_eps),
 all in 32-bit, and runs
 
@@ -78,17 +79,17 @@ class DeltaRuleMixer(Mixer):
         proj = ctx.workspace.get("delta.proj", (T, self.stacked.shape[0]), rt.dtype)
         k.linear(x, self.stacked, proj)
         o = ctx.workspace.get("delta.o", (T, width), torch.float32)
-        logits = None
+        logits = ctx.workspace.get("delta.decay_logits", (T, width), torch.float32)
         if T > self.LOGITS_BY_PRODUCT_FROM:
-            # many tokens: tanh(low) W2^T is a matrix product of its own (the recurrence would add up
-            # rank terms per token and channel, one token after the other)
+            # many tokens: tanh(low) W2^T is a matrix product on the tensor cores
             low = ctx.workspace.get("delta.low", (T, s.decay_rank), rt.dtype)
             k.cast_rows(proj[:, 5 * width:], low, activation="tanh")
-            logits = ctx.workspace.get("delta.decay_logits", (T, width), torch.float32)
             k.linear(low, self.decay_out_matrix, logits)
-        k.delta_rule(proj, self.decay_out, self.decay_bias, self.removal_bias, cache.arrays["state"], o,
+        else:
+            k.decay_logits(proj[:, 5 * width:], self.decay_out, logits)
+        k.delta_rule(proj, logits, self.decay_bias, self.removal_bias, cache.arrays["state"], o,
                      ctx.q_start, ctx.state_slots, s.num_heads, s.head_dim, s.decay_rank, s.decay_scale,
-                     s.key_eps, ctx.max_q_len, decay_logits=logits)
+                     s.key_eps, ctx.max_q_len)
         gated = ctx.workspace.get("delta.gated", (T, width), rt.dtype)
         k.gated_group_norm(o, proj[:, 3 * width:4 * width], self.norm_weight, s.norm_eps, s.head_dim, gated)
         return k.linear(gated, self.o_proj, residual, residual=residual, defer=True)

@@ -178,17 +178,19 @@ class ReferenceKernels:
             if keep:
                 history[slot, :keep] = seq[seq.shape[0] - keep:].to(history.dtype)
 
-    def delta_rule(self, proj, decay_out, decay_bias, removal_bias, state, o, q_start, state_slots, heads, d,
-                   rank, decay_scale, key_eps, max_q_len, decay_logits=None):
-        """proj [T, 5 * heads * d + rank] = r | k | v | gate | removal | low; decay_out
-        [rank, heads * d]; state [slots, heads, d, d] (value index first); o [T, heads * d]
+    def decay_logits(self, low, w2t, out):
+        self._count("decay_logits")
+        out.copy_(torch.tanh(low.float()) @ w2t.float())
+
+    def delta_rule(self, proj, decay_logits, decay_bias, removal_bias, state, o, q_start, state_slots, heads, d,
+                   rank, decay_scale, key_eps, max_q_len):
+        """proj [T, 5 * heads * d + rank] = r | k | v | gate | removal | low; decay_logits
+        [T, heads * d]; state [slots, heads, d, d] (value index first); o [T, heads * d]
         32-bit."""
         self._count("delta_rule")
         W = heads * d
         p = proj.float()
-        low = torch.tanh(p[:, 5 * W:5 * W + rank])
-        logits = low @ decay_out.float() if decay_logits is None else decay_logits.float()
-        decay = torch.exp(-decay_scale * torch.sigmoid(logits + decay_bias.float()))
+        decay = torch.exp(-decay_scale * torch.sigmoid(decay_logits.float() + decay_bias.float()))
         rate = torch.sigmoid(p[:, 4 * W:5 * W] + removal_bias.float())
         for s in range(state_slots.numel()):
             slot = int(state_slots[s])

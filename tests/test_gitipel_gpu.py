@@ -117,7 +117,7 @@ def test_delta_rule_kernel(kernels, dtype, heads, d, rank):
     scale, eps = math.exp(-0.5), 1e-6
     refs = [delta_reference(p, w2, w0, ab, heads, d, rank, scale, eps) for p in projs]
     state = torch.full((3, heads, d, d), float("nan"), dtype=torch.float32, device=DEV)
-    # the third round hands the kernel the decay's logits ready made (what a step of many tokens does)
+    # the decay's logits come from the small kernel, in the third round ready made (as a step of many tokens has them)
     for sizes, ready in (([64], False), ([1, 2, 5, 17], False), ([64], True)):
         state[:] = 0
         got = [torch.zeros(n, W) for n in lengths]
@@ -126,9 +126,13 @@ def test_delta_rule_kernel(kernels, dtype, heads, d, rank):
             q_start = torch.tensor(np.cumsum([0] + [b - a for _, a, b in step]), dtype=torch.int32, device=DEV)
             slot_t = torch.tensor([slots[s] for s, _, _ in step], dtype=torch.int32, device=DEV)
             o = torch.empty(proj.shape[0], W, dtype=torch.float32, device=DEV)
-            logits = (torch.tanh(proj[:, 5 * W:].double().cpu()) @ w2.double().t()).float().to(DEV) if ready else None
-            kernels.delta_rule(proj, w2.t().contiguous().to(DEV), w0.to(DEV), ab.to(DEV), state, o, q_start, slot_t, heads, d, rank,
-                               scale, eps, max(b - a for _, a, b in step), decay_logits=logits)
+            logits = torch.empty(proj.shape[0], W, dtype=torch.float32, device=DEV)
+            if ready:
+                logits.copy_((torch.tanh(proj[:, 5 * W:].double().cpu()) @ w2.double().t()).float())
+            else:
+                kernels.decay_logits(proj[:, 5 * W:], w2.t().contiguous().to(DEV), logits)
+            kernels.delta_rule(proj, logits, w0.to(DEV), ab.to(DEV), state, o, q_start, slot_t, heads, d, rank,
+                               scale, eps, max(b - a for _, a, b in step))
             at = 0
             for s, a, b in step:
                 got[s][a:b] = o[at:at + b - a].cpu()
@@ -159,7 +163,7 @@ def test_delta_rule_forgets_and_removes(kernels):
         state = torch.zeros(1, 1, d, d, device=DEV)
         o = torch.empty(T, W, device=DEV)
         q_start = torch.tensor([0, T], dtype=torch.int32, device=DEV)
-        kernels.delta_rule(proj.to(DEV), w2.t().contiguous().to(DEV), w0.to(DEV), ab.to(DEV), state, o, q_start,
+        kernels.delta_rule(proj.to(DEV), torch.zeros(T, W, device=DEV), w0.to(DEV), ab.to(DEV), state, o, q_start,
                            torch.zeros(1, dtype=torch.int32, device=DEV), 1, d, 1, math.exp(-0.5), 1e-6, T)
         ref, _ = delta_reference(proj, w2, w0, ab, 1, d, 1, math.exp(-0.5), 1e-6)
         close(o[:T - 1], ref[:T - 1, 0], 1e-5, "delta rule, the tokens before the last")
