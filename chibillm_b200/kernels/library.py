@@ -46,7 +46,7 @@ _SIGNATURES = {
         "chibi_qk_norm_rope_append_partial": [P, I, L, L, P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I,
                                               I, I, F, F, I, P, P],
         "chibi_attention_generic": [P, I, P, P, I, P, P, I, P, P, P, P, P, L, I, I, I, I, I, F, I, F, P, P, P, P],
-        "chibi_short_conv": [P, I, L, P, P, P, L, P, P, I, I, I, I, P],
+        "chibi_short_conv": [P, I, L, P, P, P, P, L, P, P, I, I, I, I, P],
         "chibi_delta_rule": [P, I, L, P, P, P, P, P, P, P, I, I, I, I, I, F, F, P],
         "chibi_decay_logits": [P, I, L, P, P, L, I, I, P],
         "chibi_gated_group_norm": [P, P, I, L, P, P, I, L, I, I, F, P],

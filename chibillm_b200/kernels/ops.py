@@ -954,11 +954,13 @@ class CudaKernels:
 
     # ---- parts with a fixed-size state, and the row-wise helpers around them
     def short_conv(self, x: torch.Tensor, weight: torch.Tensor, history: torch.Tensor, out: torch.Tensor,
-                   q_start: torch.Tensor, positions: torch.Tensor, state_slots: torch.Tensor, max_q_len: int) -> None:
+                   q_start: torch.Tensor, positions: torch.Tensor, state_slots: torch.Tensor, max_q_len: int,
+                   weight_t: Optional[torch.Tensor] = None) -> None:
         """out_t = x_t + sum_j weight[:, j] * x_(t - taps + 1 + j) along each sequence of
         the step.  ``history`` [slots, max(taps - 1, 1), D] (x's type, oldest first)
         gives what lies before a sequence's first token of the step and takes the
-        sequence's last taps - 1 inputs."""
+        sequence's last taps - 1 inputs.  ``weight_t`` (the weight transposed,
+        [taps, D]) lets the kernel with 16 bytes of channels per thread run."""
         _need_cuda(x, weight, history, out, q_start, state_slots)
         _rows_contiguous(x, "short_conv: x")
         _rows_contiguous(out, "short_conv: out")
@@ -969,8 +971,12 @@ class CudaKernels:
                 or not history.is_contiguous() or tuple(history.shape[1:]) != (max(taps - 1, 1), D) \
                 or out.data_ptr() == x.data_ptr():
             raise KernelError("short_conv: weight float32 [D, taps], history [slots, taps - 1, D] and out of x's type")
+        if weight_t is not None and (weight_t.dtype != torch.float32 or weight_t.shape != (taps, D)
+                                     or not weight_t.is_contiguous() or not weight_t.is_cuda):
+            raise KernelError("short_conv: weight_t must be the weight transposed, contiguous float32 [taps, D]")
         self.launches += 1
-        _check(self.lib.chibi_short_conv(_ptr(x), _code(x), x.stride(0), _ptr(weight), _ptr(history), _ptr(out),
+        _check(self.lib.chibi_short_conv(_ptr(x), _code(x), x.stride(0), _ptr(weight), _ptr(weight_t), _ptr(history),
+                                         _ptr(out),
                                          out.stride(0), _ptr(q_start), _ptr(state_slots), state_slots.numel(),
                                          int(max_q_len), D, taps, self._stream()), "short_conv")
 

@@ -21,12 +21,14 @@ class ShortConv(Part):
         self.weight_name = weight_name
         self.runtime = runtime
         self.weight: torch.Tensor = None
+        self.weight_t: torch.Tensor = None          # [taps, size], for the kernel's wide loads
 
     def expected_tensors(self) -> List[TensorSpec]:
         return [TensorSpec(self.weight_name, (self.spec.size, self.spec.taps), init=("normal", 0.0, 0.1))]
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors[self.weight_name].float().contiguous()
+        self.weight_t = self.weight.t().contiguous()
 
     def cache_need(self):
         return FixedStateNeed((("history", (max(self.spec.taps - 1, 1), self.spec.size), None),))
@@ -36,4 +38,4 @@ class ShortConv(Part):
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, ctx, state) -> None:
         self.runtime.kernels.short_conv(x, self.weight, state.arrays["history"], out, ctx.q_start, ctx.positions,
-                                        ctx.state_slots, ctx.max_q_len)
+                                        ctx.state_slots, ctx.max_q_len, weight_t=self.weight_t)

@@ -159,7 +159,7 @@ class ReferenceKernels:
             raise ValueError(kind)
         x.copy_(y.to(x.dtype))
 
-    def short_conv(self, x, weight, history, out, q_start, positions, state_slots, max_q_len):
+    def short_conv(self, x, weight, history, out, q_start, positions, state_slots, max_q_len, weight_t=None):
         """y_t = x_t + sum_j w[:, j] x_(t - taps + 1 + j); what lies before a step's
         first token comes from ``history`` [slots, taps - 1, D] (oldest first), which
         then takes the sequence's last taps - 1 inputs."""
