@@ -498,6 +498,22 @@ __global__ void activation_kernel(TX* __restrict__ x, long long total, int kind)
         x[i] = from_f32<TX>(activate(to_f32(x[i]), kind));
 }
 
+// bfloat16, eight values a thread; the result is rounded to bfloat16 at once, so the exact gelu may
+// take the cheaper formula (activate_rounded)
+__global__ void activation_bf16x8_kernel(__nv_bfloat16* __restrict__ x, long long groups, int kind)
+{
+    pdl_enter();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < groups;
+         i += (long long)gridDim.x * blockDim.x) {
+        float v[8];
+        Pack<__nv_bfloat16>::load(x + 8 * i, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            v[e] = activate_rounded(v[e], kind);
+        Pack<__nv_bfloat16>::store(x + 8 * i, v);
+    }
+}
+
 // out = act(sum over the splits of a split product's partial sums [splits][total])
 template <typename TO>
 __global__ void reduce_activation_kernel(const float* __restrict__ partial, int splits, long long total,
@@ -699,6 +715,11 @@ CHIBI_API int chibi_activation(void* x, int x_type, long long total, int kind, c
         return CHIBI_OK;
     if (kind < 0 || kind > 4)
         return CHIBI_ERR_ARGUMENT;
+    if (x_type == CHIBI_BF16 && total % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        launch(activation_bf16x8_kernel, dim3(blocks_for(total / 8, 256)), dim3(256), 0, stream, (__nv_bfloat16*)x,
+               total / 8, kind);
+        return launch_status();
+    }
     CHIBI_DISPATCH_TYPE(x_type, TX, {
         launch(activation_kernel<TX>, dim3(blocks_for(total, 256)), dim3(256), 0, stream, (TX*)x, total, kind);
     });

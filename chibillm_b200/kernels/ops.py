@@ -184,6 +184,8 @@ class CudaKernels:
         self.few_rows_max = int(self.lib.chibi_gemm_few_rows_max())
         self.fold_norms = True
         self.fold_heads = True           # many rows: the q | k | v product finishes its heads itself
+        # many rows: an activation in the product's epilogue (True), or a kernel of its own after it
+        self.fold_activation = False
         # The K range of a product with few rows is split over CTAs.  Their partial sums go through
         # global scratch to a second kernel that also does what follows the product.
         self.fuse_split_products = True
@@ -1091,9 +1093,11 @@ class CudaKernels:
         if kind not in self.ACTIVATIONS:
             raise KernelError(f"linear_activation: one of {sorted(self.ACTIVATIONS)}")
         if isinstance(x, ScaledRows):
-            return kind in self._EPILOGUE_ACTIVATIONS and self._linear_of_scaled(x, w, out, swiglu=False,
-                                                                                  activation=kind)
+            return self.fold_activation and kind in self._EPILOGUE_ACTIVATIONS \
+                and self._linear_of_scaled(x, w, out, swiglu=False, activation=kind)
         pending = self.linear_partial(x, w)
+        if pending is None and not self.fold_activation:
+            return False
         if pending is None:
             # many rows: the activation is the product's epilogue
             M, K = x.shape
