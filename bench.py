@@ -386,7 +386,7 @@ def gitipel_config(width, heads, kv_heads, dim, ff, vocab=32768):
     """Four layers, attention and delta rule in turn, the first two run twice: six layer
     runs.  Delta-rule heads of 64 channels over the whole width, a decay input of rank 64."""
     att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim,
-                                          "scale": dim ** -0.5, "softcap": 50.0}, "mlp": {"kind": "dense", "ff": ff}}
+                                          "scale": dim ** -0.5, "softcap": 30.0}, "mlp": {"kind": "dense", "ff": ff}}
     rec = {"type": "general_delta", "mixer": {"heads": width // 64, "dim": 64, "rank": 64},
            "mlp": {"kind": "dense", "ff": ff}}
     return {"architecture": "Gitipel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
