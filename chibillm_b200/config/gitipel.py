@@ -66,8 +66,8 @@ class GitipelConfig:
         vocab = r.positive_int("vocab")
         width = r.positive_int("width")
         eps = KeyReader(_object(r, "norm")).positive_float("eps")
-        embedding_scale = KeyReader(_object(r, "embedding")).positive_float("scale") if r.has("embedding") else 1.0
-        logit_scale = r.positive_float("logit_scale") if r.has("logit_scale") else 1.0
+        embedding_scale = _number(KeyReader(_object(r, "embedding")), "scale") if r.has("embedding") else 1.0
+        logit_scale = _number(r, "logit_scale") if r.has("logit_scale") else 1.0
         taps = KeyReader(_object(r, "canon")).positive_int("taps") if r.has("canon") else None
         shapes = obj.get(SHAPES_KEY) or {}
         raw_layers = r.raw("layers")
@@ -159,6 +159,14 @@ class GitipelConfig:
             input_adapters=(AdapterSpec(kind="scale", params=(("factor", self.embedding_scale),)),),
             logit_adapters=(AdapterSpec(kind="scale", params=(("factor", self.logit_scale),)),),
             stream_adapters=stream)
+
+
+def _number(reader: KeyReader, key: str) -> float:
+    """A finite number of either sign (a scale)."""
+    v = reader.raw(key)
+    if isinstance(v, bool) or not isinstance(v, (int, float)) or not math.isfinite(v):
+        raise ConfigError("invalid_field", f"key '{key}' must be a finite number, got {v!r}")
+    return float(v)
 
 
 def _object(reader: KeyReader, key: str) -> dict:

@@ -109,6 +109,8 @@ __device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_byte_a
     return d;
 }
 
+// OPT: the instantiation with the options of the score; the plain one is compiled without them.
+template <bool OPT>
 __global__ void __launch_bounds__(ATC_THREADS)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const AttnTcParams p)
@@ -307,7 +309,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         // with options the scores are brought to their final form (in units of log2) right after
         // they are read, and the scale below is 1
-        const bool options = p.softcap > 0.f || p.bias_r1 != nullptr;
+        constexpr bool options = OPT;
         const float sl2 = options ? 1.f : p.scale_log2;
         const int bias_head = kv_head * p.group + (live ? r - tok * p.group : 0);
         const float r1 = p.bias_r1 ? p.bias_r1[bias_head] : 0.f, r2 = p.bias_r1 ? p.bias_r2[bias_head] : 0.f;
@@ -555,6 +557,7 @@ constexpr int SMEM2_TILES = 2 * Q_BYTES + 4 * KV_TILE_BYTES;
 constexpr int NUM_BARS2 = 14;
 constexpr size_t ATC2_SMEM = SMEM2_TILES + NUM_BARS2 * 8 + 16 + 1024;
 
+template <bool OPT>
 __global__ void __launch_bounds__(ATC2_THREADS, 1)
 attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                         const AttnTcParams p)
@@ -761,6 +764,13 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         const uint32_t o_addr = lane_addr + 256 + q * 128;
         const int my_tiles = nt[q];
         float m = -INFINITY, l = 0.f;
+        // options of the score: both passes over the row bring their piece to its final form (in
+        // units of log2) right after it is read, and the scale below is 1
+        constexpr bool options = OPT;
+        const float sl2 = options ? 1.f : p.scale_log2;
+        const int bias_head = kv_head * p.group + (live ? r - tok * p.group : 0);
+        const float r1 = p.bias_r1 ? p.bias_r1[bias_head] : 0.f, r2 = p.bias_r1 ? p.bias_r2[bias_head] : 0.f;
+        const float two_over_cap_log2 = p.softcap > 0.f ? 2.f * 1.4426950408889634f / p.softcap : 0.f;
         for (int j = 0; j < my_tiles; ++j) {
             const int st = j & 1;
             const int key0 = key_begin + j * KEYS;
@@ -771,7 +781,22 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             // while this one is worked on): the maximum, then P = exp2(S * scale - m) as packed
             // bfloat16 pairs, which overwrite the columns of S already read.
             const bool masked = __any_sync(0xffffffffu, key0 + KEYS - 1 > pos || key0 < first);
-            auto mask_piece = [&](uint32_t (&v)[32], int c0) {
+            // With options the first pass brings a piece to its final form and writes it back to its
+            // columns; the second pass reads finished (and masked) scores and changes nothing.
+            auto mask_piece = [&](uint32_t (&v)[32], int c0, bool second = false) {
+                if (options && second)
+                    return;
+                if (options) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float x = __uint_as_float(v[i]) * p.scale;
+                        if (p.softcap > 0.f)
+                            x = p.softcap * (1.f - __fdividef(2.f, fast_exp2(x * two_over_cap_log2) + 1.f));
+                        const int dist = pos - (key0 + c0 + i);
+                        x -= r1 * __logf(1.f + r2 * (float)(dist > 0 ? dist : 0));
+                        v[i] = __float_as_uint(x * 1.4426950408889634f);
+                    }
+                }
                 if (masked) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
@@ -789,6 +814,8 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 tmem_load_wait();
                 tmem_load_32x32(s_addr + c0 + 32, pb);
                 mask_piece(pa, c0);
+                if (options)
+                    tmem_store_32x32(s_addr + c0, pa);
 #pragma unroll
                 for (int i = 0; i < 32; ++i)
                     mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(pa[i]));
@@ -796,13 +823,17 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 if (c0 + 64 < KEYS)
                     tmem_load_32x32(s_addr + c0 + 64, pa);
                 mask_piece(pb, c0 + 32);
+                if (options)
+                    tmem_store_32x32(s_addr + c0 + 32, pb);
 #pragma unroll
                 for (int i = 0; i < 32; ++i)
                     mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(pb[i]));
             }
+            if (options)
+                tmem_store_wait();                           // the finished scores are in their columns
             tmem_load_32x32(s_addr, pa);                     // the second pass starts while the maximum settles
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-            mx *= p.scale_log2;                              // the scale is positive
+            mx *= sl2;                                     // the scale is positive
             const bool grow = mx > m + 8.f;                  // also true for the first visible key (m = -inf)
             if (__any_sync(0xffffffffu, grow && m != -INFINITY && j > 0)) {
                 // rescale what has accumulated: the product of tile j-1 must have landed first
@@ -818,12 +849,12 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             const float base = m == -INFINITY ? 0.f : m;
             float sum4[4] = { 0.f, 0.f, 0.f, 0.f };
             auto exp_piece = [&](uint32_t (&v)[32], int c0) {
-                mask_piece(v, c0);
+                mask_piece(v, c0, true);
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), p.scale_log2, -base));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), p.scale_log2, -base));
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), sl2, -base));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), sl2, -base));
                     sum4[i & 3] += p0 + p1;
                     const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                     packed[i] = *reinterpret_cast<const uint32_t*>(&h);
@@ -918,11 +949,7 @@ CHIBI_API int chibi_attention_prefill_tc(const void* q, const void* k_cache, con
     if (nkv <= 0 || nq % nkv != 0 || window < 0 || variant < 0 || variant > 2 || softcap < 0.f
         || (bias_r1 != nullptr) != (bias_r2 != nullptr))
         return CHIBI_ERR_ARGUMENT;
-    if (softcap > 0.f || bias_r1) {
-        if (variant == 2)
-            return CHIBI_ERR_UNSUPPORTED;
-        variant = 1;                   // the kernel with one query tile per CTA has the options
-    }
+
     if (page_size < 8 || page_size > 128 || KEYS % page_size != 0
         || (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15)
         || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
@@ -950,14 +977,18 @@ CHIBI_API int chibi_attention_prefill_tc(const void* q, const void* k_cache, con
     p.softcap = softcap;
     p.bias_r1 = bias_r1;
     p.bias_r2 = bias_r2;
+    const bool with_options = softcap > 0.f || bias_r1 != nullptr;
     CUtensorMap mk, mv;
     if (!tensor_map_2d(k_cache, p.cache_rows, D, D, page_size, &mk)
         || !tensor_map_2d(v_cache, p.cache_rows, D, D, page_size, &mv))
         return CHIBI_ERR_UNSUPPORTED;
     static bool configured = false;
     if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   (int)ATC_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)ATC_SMEM);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)ATC_SMEM);
         if (e != cudaSuccess)
             return (int)e;
         configured = true;
@@ -972,14 +1003,20 @@ CHIBI_API int chibi_attention_prefill_tc(const void* q, const void* k_cache, con
     if (variant == 2 || (variant == 0 && ctas2 >= sms)) {
         static bool configured2 = false;
         if (!configured2) {
-            const cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc2_kernel,
-                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATC2_SMEM);
+            cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc2_kernel<false>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATC2_SMEM);
+            if (e == cudaSuccess)
+                e = cudaFuncSetAttribute(attn_prefill_tc2_kernel<true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ATC2_SMEM);
             if (e != cudaSuccess)
                 return (int)e;
             configured2 = true;
         }
         const dim3 grid2((unsigned)((rows + 2 * ROWS - 1) / (2 * ROWS)), nkv, seqs);
-        launch(attn_prefill_tc2_kernel, grid2, dim3(ATC2_THREADS), ATC2_SMEM, stream, mk, mv, p);
+        if (with_options)
+            launch(attn_prefill_tc2_kernel<true>, grid2, dim3(ATC2_THREADS), ATC2_SMEM, stream, mk, mv, p);
+        else
+            launch(attn_prefill_tc2_kernel<false>, grid2, dim3(ATC2_THREADS), ATC2_SMEM, stream, mk, mv, p);
         return launch_status();
     }
     if (kv_splits > 1) {
@@ -992,7 +1029,10 @@ CHIBI_API int chibi_attention_prefill_tc(const void* q, const void* k_cache, con
         p.part_ml = scratch + (size_t)tokens * nq * kv_splits * D;
     }
     const dim3 grid((unsigned)((rows + ROWS - 1) / ROWS), nkv, seqs * p.kv_splits);
-    launch(attn_prefill_tc_kernel, grid, dim3(ATC_THREADS), ATC_SMEM, stream, mk, mv, p);
+    if (with_options)
+        launch(attn_prefill_tc_kernel<true>, grid, dim3(ATC_THREADS), ATC_SMEM, stream, mk, mv, p);
+    else
+        launch(attn_prefill_tc_kernel<false>, grid, dim3(ATC_THREADS), ATC_SMEM, stream, mk, mv, p);
     int st = launch_status();
     if (st == CHIBI_OK && p.kv_splits > 1) {
         launch(attn_prefill_merge_kernel, dim3(nq, max_q_len, seqs), dim3(D), 0, stream, p);

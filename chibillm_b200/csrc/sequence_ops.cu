@@ -452,6 +452,59 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ x, const TG* _
         dst[j] = from_f32<TO>(src[j] * inv * weight[g * n + j] * sigmoidf_(to_f32(gr[j])));
 }
 
+// Groups of 32, 64 or 128 features: LANES = n / 4 threads side by side own a group, four features
+// each (16-byte loads of x and the weight), so a warp takes 32 / LANES groups at once.
+template <typename T> struct Four;
+template <> struct Four<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) { Pack<float>::load(p, v); }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) { Pack<float>::store(p, v); }
+};
+template <> struct Four<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4])
+    {
+        const uint2 q = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+        v[0] = __low2float(h[0]); v[1] = __high2float(h[0]); v[2] = __low2float(h[1]); v[3] = __high2float(h[1]);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4])
+    {
+        uint2 q;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+        h[0] = __floats2bfloat162_rn(v[0], v[1]);
+        h[1] = __floats2bfloat162_rn(v[2], v[3]);
+        *reinterpret_cast<uint2*>(p) = q;
+    }
+};
+
+template <int LANES, typename TG, typename TO>
+__global__ void __launch_bounds__(256)
+gated_group_norm_four_kernel(const float* __restrict__ x, const TG* __restrict__ gate, long long gate_stride,
+                             const float* __restrict__ weight, TO* __restrict__ out, long long rows, int groups,
+                             float eps)
+{
+    pdl_enter();
+    constexpr int n = 4 * LANES;
+    const long long job = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LANES;
+    const int sub = threadIdx.x % LANES;
+    const bool live = job < rows * groups;            // whole sub-groups are live or not; shuffles need all lanes
+    const long long row = live ? job / groups : 0;
+    const int g = live ? (int)(job - row * groups) : 0;
+    float v[4], gt[4], w[4];
+    Four<float>::load(x + ((size_t)row * groups + g) * n + 4 * sub, v);
+    Four<TG>::load(gate + (size_t)row * gate_stride + (size_t)g * n + 4 * sub, gt);
+    Four<float>::load(weight + (size_t)g * n + 4 * sub, w);
+    float s = fmaf(v[0], v[0], fmaf(v[1], v[1], fmaf(v[2], v[2], v[3] * v[3])));
+#pragma unroll
+    for (int step = 1; step < LANES; step <<= 1)
+        s += __shfl_xor_sync(0xffffffffu, s, step);
+    const float inv = 1.f / sqrtf(s / (float)n + eps);
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+        v[e] = v[e] * inv * w[e] * sigmoidf_(gt[e]);
+    if (live)
+        Four<TO>::store(out + ((size_t)row * groups + g) * n + 4 * sub, v);
+}
+
 // ---------------------------------------------------------------- row-wise helpers
 __global__ void scale_kernel(float* __restrict__ x, float factor, long long total)
 {
@@ -670,6 +723,25 @@ CHIBI_API int chibi_gated_group_norm(const float* x, const void* gate, int gate_
     const long long blocks = (jobs + 3) / 4;
     if (blocks > 2147483647LL)
         return CHIBI_ERR_UNSUPPORTED;
+    const int per_gate = gate_type == CHIBI_BF16 ? 8 : 16, per_out = out_type == CHIBI_BF16 ? 8 : 16;
+    if ((n == 32 || n == 64 || n == 128) && gate_stride % 4 == 0
+        && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(weight) & 15) == 0
+        && (reinterpret_cast<uintptr_t>(gate) % per_gate) == 0 && (reinterpret_cast<uintptr_t>(out) % per_out) == 0) {
+        const long long threads = jobs * (n / 4);
+        const dim3 grid((unsigned)((threads + 255) / 256));
+        CHIBI_DISPATCH_TYPE(gate_type, TG, CHIBI_DISPATCH_TYPE(out_type, TO, {
+            if (n == 32)
+                launch(gated_group_norm_four_kernel<8, TG, TO>, grid, dim3(256), 0, stream, x, (const TG*)gate,
+                       gate_stride, weight, (TO*)out, rows, groups, eps);
+            else if (n == 64)
+                launch(gated_group_norm_four_kernel<16, TG, TO>, grid, dim3(256), 0, stream, x, (const TG*)gate,
+                       gate_stride, weight, (TO*)out, rows, groups, eps);
+            else
+                launch(gated_group_norm_four_kernel<32, TG, TO>, grid, dim3(256), 0, stream, x, (const TG*)gate,
+                       gate_stride, weight, (TO*)out, rows, groups, eps);
+        }));
+        return launch_status();
+    }
     CHIBI_DISPATCH_TYPE(gate_type, TG, CHIBI_DISPATCH_TYPE(out_type, TO, {
         launch(gated_group_norm_kernel<TG, TO>, dim3((unsigned)blocks), dim3(128), 0, stream, x, (const TG*)gate,
                gate_stride, weight, (TO*)out, rows, groups, n, eps);

@@ -841,7 +841,6 @@ class CudaKernels:
             lib = self._attention_libs[d] = self._profiled(lib)
         seqs = ctx_len.numel()
         mode = 1 if max_q_len == 1 else (2 if min_q_len > 1 else 3)
-        options = softcap != 0.0 or bias_r1 is not None
         if mode & 2 and self.use_tcgen05_attention and d in build.TCGEN05_ATTENTION_HEAD_DIMS \
                 and page_size >= 8 and 128 % page_size == 0:
             # prompt portions on tcgen05; one-token sequences stay with the split-key kernel
@@ -857,7 +856,7 @@ class CudaKernels:
                 _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
                 _ptr(seq_rows), _ptr(q_start), _ptr(ctx_len), seqs, nq, nkv, page_size, k_cache.shape[0],
                 float(scale), int(window or 0), 1 if mode & 1 else 0, int(max_q_len),
-                1 if options else int(self.tcgen05_attention_variant), kv_splits, _ptr(part),
+                int(self.tcgen05_attention_variant), kv_splits, _ptr(part),
                 part.numel() if part is not None else 0, q.shape[0], float(softcap), _ptr(bias_r1), _ptr(bias_r2),
                 _ptr(self.error), self._stream())
             if status == 0:

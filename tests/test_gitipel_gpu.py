@@ -183,7 +183,7 @@ def test_delta_rule_forgets_and_removes(kernels):
 def test_gated_group_norm_kernel(kernels, dtype):
     g = torch.Generator().manual_seed(0)
     dt = DTYPES[dtype]
-    for heads, d in ((3, 16), (2, 48), (1, 200)):
+    for heads, d in ((3, 16), (2, 48), (1, 200), (3, 32), (2, 64), (1, 128)):
         T, W = 11, heads * d
         x = torch.randn(T, W, generator=g) * 3
         wide = torch.randn(T, 3 * W + 5, generator=g).to(dt)       # the gate is a column range of a wider array
@@ -283,9 +283,16 @@ def test_attention_with_cap_bias_and_tied_values(kernels, dtype, H, G, d):
         ref = plain.capped_distance_scores(q.double(), k.double(), r1.double() if bias else torch.zeros(H).double(),
                                            r2.double(), scale, softcap)
         tol = 2e-5 if dtype == "float32" else 2e-2
-        whole = run_attention(kernels, q, k, r1 if bias else None, r2 if bias else None, scale, softcap, dtype, page_size,
-                              [(0, T)])
-        close(whole, ref, tol, f"attention whole cap {softcap} bias {bias}")
+        # head sizes 64 and 128 in bfloat16 run prompts on tcgen05: both of its kernels (one and two
+        # query tiles per CTA) are asked for in turn; 0 leaves the choice to the kernels
+        for variant in ((1, 2) if dtype == "bfloat16" and d in (64, 128) else (0,)):
+            kernels.tcgen05_attention_variant = variant
+            try:
+                whole = run_attention(kernels, q, k, r1 if bias else None, r2 if bias else None, scale, softcap, dtype,
+                                      page_size, [(0, T)])
+            finally:
+                kernels.tcgen05_attention_variant = 0
+            close(whole, ref, tol, f"attention whole cap {softcap} bias {bias} variant {variant}")
         cut_up = run_attention(kernels, q, k, r1 if bias else None, r2 if bias else None, scale, softcap, dtype,
                                page_size, [(0, 61), (61, 63), (63, 64), (64, 130)] + [(i, i + 1) for i in range(130, T)])
         close(cut_up, ref, tol, f"attention portions and single tokens cap {softcap} bias {bias}")
