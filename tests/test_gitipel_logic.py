@@ -221,3 +221,21 @@ def test_command_line_and_scheduler_on_cpu(tmp_path):
             top = torch.topk(row, 2).values
             if float(top[0] - top[1]) > 1e-4 * float(row.abs().max()):
                 assert int(torch.argmax(row)) == tok
+
+
+def test_a_model_of_recurrent_layers_only_runs_without_a_paged_cache(tmp_path):
+    """No attention layer at all: the cache plan has no page group, requests hold
+    state slots only; a looped layer has a state of its own per pass."""
+    cfg = {"architecture": "Gitipel", "vocab": 97, "width": 48, "norm": {"eps": 1e-5}, "canon": {"taps": 2},
+           "layers": [gitipel_models.delta(2, 16, 4, ff=64), gitipel_models.delta(1, 32, 3)],
+           "loop": {"start": 1, "stop": 2, "times": 2}}
+    folder = gitipel_models.write_model(cfg, str(tmp_path / "m"), seed=3)
+    reqs = helpers.random_requests(97, [5, 19, 33], seed=1)
+    ref = gitipel_models.plain_logits(cfg, 3, reqs)
+    runner = cpu_runner(folder, 16, 64)
+    assert runner.plan.groups == () and len(runner.storage.state_views()) == 6      # 3 layer runs x (state, history)
+    for trace, what in ((helpers.trace_whole(reqs), "whole"), (helpers.trace_portions(reqs, seed=2), "portions"),
+                        (helpers.trace_mixed(reqs, 128, seed=1, decode_tail=4), "mixed")):
+        got = helpers.run_trace(runner, trace)
+        helpers.assert_logits_close(got, ref, helpers.TOL["float32"], f"gitipel recurrent only {what}")
+    assert not runner.cache.requests
