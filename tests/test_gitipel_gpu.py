@@ -447,3 +447,25 @@ def test_trace_program(folders, tmp_path):
             got = torch.from_numpy(np.fromfile(os.path.join(out_dir, f"{i}.f32"), dtype="<f4").reshape(len(rows), -1))
             scale = float(torch.stack(rows).abs().max())
             assert float((got - torch.stack(rows)).abs().max()) <= helpers.TOL[dtype] * scale
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_recurrent_layers_only(tmp_path, dtype):
+    """A model without any attention layer: no page group, state slots only."""
+    cfg = {"architecture": "Gitipel", "vocab": 97, "width": 64, "norm": {"eps": 1e-5}, "canon": {"taps": 2},
+           "layers": [gitipel_models.delta(2, 32, 4, ff=64), gitipel_models.delta(1, 64, 8)],
+           "loop": {"start": 1, "stop": 2, "times": 2}}
+    folder = gitipel_models.write_model(cfg, str(tmp_path / "m"), seed=3)
+    reqs = helpers.random_requests(97, [5, 70, 133], seed=1)
+    ref = gitipel_models.plain_logits(cfg, 3, reqs, torch.float32)
+    runner = make_runner(folder, dtype, 16, 192)
+    assert runner.plan.groups == ()
+    for trace, what in ((helpers.trace_whole(reqs), "whole"), (helpers.trace_last_decoded(reqs, 20), "decoded"),
+                        (helpers.trace_mixed(reqs, 256, seed=1, decode_tail=6), "mixed")):
+        got = helpers.run_trace(runner, trace)
+        # bfloat16: twice the usual limit.  At a sequence's first positions the state holds one or two
+        # outer products and the per-head norm divides o by its own small size, so the rounding of r, k
+        # and v shows in full (32-bit: 1.4e-6 in every trace; bfloat16: 2.5e-2 whole, 3.4e-2 mixed).
+        tol = helpers.TOL[dtype] * (2 if dtype == "bfloat16" else 1)
+        helpers.assert_logits_close(got, ref, tol, f"gitipel recurrent only {dtype} {what}")
+    assert not runner.cache.requests
