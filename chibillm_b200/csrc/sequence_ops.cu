@@ -5,9 +5,11 @@
 //   inputs before a step's first token taken from the request's history;
 // * delta_rule: the recurrence S <- diag(w) S - (a u)(u^T S) + k v^T, o = S^T r with one
 //   state matrix per head, decays, rates and unit keys made in 32-bit from the
-//   stacked product's output;
+//   stacked product's output and the decay's logits; decay_logits makes those logits
+//   for steps of few tokens;
 // * gated_group_norm: x / rms(x per group) * weight * sigmoid(gate);
-// * scale, cast_rows, add_row_vector, activation.
+// * scale, cast_rows (with an activation on the way), add_row_vector, activation (in place,
+//   or on the sums of a split product).
 //
 // Everything that enters the recurrence, and the state itself, is 32-bit in the
 // bfloat16 engine too.

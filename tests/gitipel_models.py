@@ -1,11 +1,12 @@
 """Small Gitipel configurations and random weights for the tests.
 
 The configurations differ from one another in every size and option: width,
-vocabulary (also an odd one), head counts and groups, head sizes (16 to 64,
-also 48), the rank of the decay input (also an odd one), taps (none, 2, 3, 5),
+vocabulary (also odd ones), head counts and groups, head sizes (16 to 128,
+also 24, 40, 48, 80 and 96), the rank of the decay input (also odd ones), taps
+(none, 2, 3, 5),
 layers without a feed-forward, layers that run once, three times, or not in a
 loop at all, a loop that starts after the first layer or covers all layers,
-caps, scales and eps.  The weights are made here, with torch's generator, and
+caps, scales (also a negative one) and eps.  The weights are made here, with torch's generator, and
 written with the ``safetensors`` library; nothing of the package takes part.
 """
 from __future__ import annotations
@@ -55,6 +56,13 @@ CONFIGS: Dict[str, dict] = {
            "layers": [attention(4, 2, 64, softcap=25.0, ff=512), delta(4, 64, 8, ff=256),
                       attention(2, 1, 128, softcap=40.0, ff=384)],
            "loop": {"start": 0, "stop": 2, "times": 2}},
+    # sizes that are no power of two anywhere: head sizes 80 and 40 (five query heads on one key
+    # head), recurrent heads of 24 and 96 channels, ranks 6 and 7, five taps, a negative scale
+    "G5": {"architecture": "Gitipel", "vocab": 257, "width": 160, "norm": {"eps": 1e-5},
+           "embedding": {"scale": -1.5}, "logit_scale": 1.0, "canon": {"taps": 5},
+           "layers": [attention(5, 1, 80, softcap=15.0, ff=200), delta(3, 24, 6, ff=120),
+                      attention(2, 2, 40, softcap=None, ff=96), delta(1, 96, 7)],
+           "loop": {"start": 2, "stop": 4, "times": 2}},
 }
 
 

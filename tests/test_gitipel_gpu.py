@@ -332,6 +332,7 @@ CASES = {
     "G2": (16, [2, 70, 131, 300], [1, 200, 33, 250, 64, 129, 7]),
     "G3": (8, [3, 64, 129, 190], [150, 20, 65, 2, 180, 99, 40]),
     "G4": (16, [5, 129, 260, 400], [400, 31, 129, 64, 350, 3, 222]),
+    "G5": (16, [4, 66, 140, 300], [300, 20, 131, 64, 150, 2, 90]),
 }
 SEED = 21
 

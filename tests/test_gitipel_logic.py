@@ -131,7 +131,7 @@ def test_plain_mechanisms_on_small_cases():
 
 # ------------------------------------------------------------------ the engine on the stand-ins
 @pytest.mark.parametrize("name,page_size,lengths", [("G1", 4, [1, 9, 30]), ("G2", 8, [2, 21, 37]),
-                                                    ("G3", 16, [3, 18, 33])])
+                                                    ("G3", 16, [3, 18, 33]), ("G5", 8, [2, 11, 34])])
 def test_cutting_and_batching_on_cpu(tmp_path, name, page_size, lengths):
     cfg = gitipel_models.get(name)
     folder = gitipel_models.write_model(cfg, str(tmp_path / name), seed=11)
