@@ -14,7 +14,7 @@
 // Everything that enters the recurrence, and the state itself, is 32-bit in the
 // bfloat16 engine too.
 #define CHIBI_UNIT sequence_ops
-#define CHIBI_UNIT_ID 7
+#define CHIBI_UNIT_ID 8
 #include "common.cuh"
 
 namespace chibi {
