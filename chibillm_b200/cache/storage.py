@@ -41,10 +41,13 @@ class CachePlan:
     # whose parts have several needs, ("several", (one of these per need, ...))
     steps: Tuple[Optional[tuple], ...]
     tied: Tuple[str, ...] = ()      # groups whose values are their keys (no value arrays)
+    value_dims: Tuple[Tuple[str, int], ...] = ()     # groups whose value heads have another size than their keys
 
 
 def group_name(need: PagedKVNeed) -> str:
     base = f"kv{need.num_kv_heads}x{need.head_dim}" if not need.tied_values else f"k{need.num_kv_heads}x{need.head_dim}"
+    if need.value_dim is not None and need.value_dim != need.head_dim:
+        base += f"v{need.value_dim}"
     return base if need.window is None else f"{base}w{need.window}"
 
 
@@ -74,8 +77,8 @@ def plan_cache(needs: Sequence[object], cache_of: Sequence[Optional[int]], page_
                 raise CacheError("invalid_configuration",
                                  f"run step {i} reads the cache of step {src}, which owns no paged cache")
             theirs = needs_of[owner[1]]
-            if (need.num_kv_heads, need.head_dim, need.tied_values) != (
-                    theirs.num_kv_heads, theirs.head_dim, theirs.tied_values):
+            if (need.num_kv_heads, need.head_dim, need.tied_values, need.value_dim or need.head_dim) != (
+                    theirs.num_kv_heads, theirs.head_dim, theirs.tied_values, theirs.value_dim or theirs.head_dim):
                 raise CacheError("invalid_configuration",
                                  f"run step {i} cannot read the cache of step {src}: shapes differ")
             if need.window != theirs.window:
@@ -111,7 +114,9 @@ def plan_cache(needs: Sequence[object], cache_of: Sequence[Optional[int]], page_
     max_blocks = (max(max_positions, 1) + page_size - 1) // page_size if max_positions else num_pages
     groups = tuple(GroupLayout(name, n.num_kv_heads, n.head_dim, n.window, page_size, num_pages,
                                entries[name], max_blocks) for name, n in needs_of.items())
-    return CachePlan(groups, tuple(steps), tuple(name for name, n in needs_of.items() if n.tied_values))
+    return CachePlan(groups, tuple(steps), tuple(name for name, n in needs_of.items() if n.tied_values),
+                     tuple((name, n.value_dim) for name, n in needs_of.items()
+                           if n.value_dim is not None and n.value_dim != n.head_dim))
 
 
 class CacheStorage:
@@ -121,12 +126,14 @@ class CacheStorage:
         self.num_slots = num_slots
         self.keys: Dict[str, torch.Tensor] = {}
         self.values: Dict[str, torch.Tensor] = {}
+        value_dims = dict(plan.value_dims)
         for g in plan.groups:
             shape = (g.num_entries, g.num_pages, g.num_kv_heads, g.page_size, g.head_dim)
             self.keys[g.name] = torch.zeros(shape, dtype=runtime.dtype, device=runtime.device)
             # a group whose values are its keys holds one array; readers get it under both names
             self.values[g.name] = self.keys[g.name] if g.name in plan.tied else \
-                torch.zeros(shape, dtype=runtime.dtype, device=runtime.device)
+                torch.zeros(shape[:4] + (value_dims.get(g.name, g.head_dim),), dtype=runtime.dtype,
+                            device=runtime.device)
         # the block tables' mirror on the device: row = a request's state slot
         self.tables: Dict[str, torch.Tensor] = {
             g.name: torch.full((num_slots, max(g.max_blocks, 1)), -1, dtype=torch.int32, device=runtime.device)

@@ -91,6 +91,21 @@ class KeyReader:
                               f"key '{key}' must be null or absent, got {self.obj[key]!r}")
 
 
+def finite_number(reader: KeyReader, key: str) -> float:
+    """A finite number of either sign (a scale)."""
+    v = reader.raw(key)
+    if isinstance(v, bool) or not isinstance(v, (int, float)) or not math.isfinite(v):
+        raise ConfigError("invalid_field", f"key '{key}' must be a finite number, got {v!r}")
+    return float(v)
+
+
+def object_at(reader: KeyReader, key: str) -> dict:
+    v = reader.raw(key)
+    if not isinstance(v, dict):
+        raise ConfigError("invalid_field", f"key '{key}' must be an object, got {v!r}")
+    return v
+
+
 def read_config_json(model_dir: str) -> dict:
     path = os.path.join(model_dir, "config.json")
     try:

@@ -27,7 +27,7 @@ import math
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
-from .base import ConfigError, KeyReader
+from .base import ConfigError, KeyReader, finite_number as _number, object_at as _object
 from .spec import (AdapterSpec, AttentionSpec, DeltaRuleSpec, DenseMLPSpec, LayerSpec, ModelSpec, NormSpec,
                    PositionSpec, RunStep, ShortConvSpec)
 
@@ -159,18 +159,3 @@ class GitipelConfig:
             input_adapters=(AdapterSpec(kind="scale", params=(("factor", self.embedding_scale),)),),
             logit_adapters=(AdapterSpec(kind="scale", params=(("factor", self.logit_scale),)),),
             stream_adapters=stream)
-
-
-def _number(reader: KeyReader, key: str) -> float:
-    """A finite number of either sign (a scale)."""
-    v = reader.raw(key)
-    if isinstance(v, bool) or not isinstance(v, (int, float)) or not math.isfinite(v):
-        raise ConfigError("invalid_field", f"key '{key}' must be a finite number, got {v!r}")
-    return float(v)
-
-
-def _object(reader: KeyReader, key: str) -> dict:
-    v = reader.raw(key)
-    if not isinstance(v, dict):
-        raise ConfigError("invalid_field", f"key '{key}' must be an object, got {v!r}")
-    return v

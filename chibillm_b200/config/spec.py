@@ -36,12 +36,25 @@ class PositionSpec:
     ``kind`` "rope": split-half rotation of the first ``rotary_dim`` features
     of every head with ``inv_freq[j] = theta ** (-2j / rotary_dim)``.
     ``kind`` "none": nothing is applied.
+
+    ``scaling_factor`` s > 0 stretches the slow frequencies for contexts longer
+    than ``original_positions`` (the YaRN rule): with
+    turn(t) = rotary_dim * ln(original_positions / (2 pi t)) / (2 ln theta),
+    lo = max(floor(turn(fast_turns)), 0), hi = min(ceil(turn(slow_turns)), rotary_dim - 1)
+    and ramp_j = clamp((j - lo) / max(hi - lo, 0.001), 0, 1), frequency j becomes
+    inv_freq[j] * (ramp_j / s + 1 - ramp_j), and cosines and sines are multiplied by
+    ``amplitude_slope`` * ln(s) + 1.  0 switches it off.
     """
 
     kind: str
     head_dim: int = 0
     rotary_dim: int = 0
     theta: float = 0.0
+    scaling_factor: float = 0.0
+    original_positions: int = 0
+    fast_turns: float = 0.0
+    slow_turns: float = 0.0
+    amplitude_slope: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -63,6 +76,14 @@ class AttentionSpec(MixerSpec):
     learned numbers per query head (tensor roles "distance_r1", "distance_r2").
     ``tied_values``: the values are the keys as projected; there is no value
     projection and the cache holds keys only.
+    ``value_dim`` (None: ``head_dim``): the size of a value head where it differs
+    from that of a query or key head.  ``chunk`` C: position i sees j <= i only
+    if floor(i / C) = floor(j / C), blocks counted from the sequence's start.
+    ``unit_norm_eps`` (None: off): after the rotation every q and k head is
+    divided by its root mean square (this eps inside the root), without a
+    weight; ``qk_norm`` by contrast comes before the rotation and has weights.
+    ``own_kv`` False: the layer has no key and value projections at all and runs
+    only as a reader of another run step's cache (``RunStep.cache_of``).
     """
 
     hidden_size: int = 0
@@ -76,6 +97,10 @@ class AttentionSpec(MixerSpec):
     softcap: Optional[float] = None
     distance_bias: Optional[str] = None
     tied_values: bool = False
+    value_dim: Optional[int] = None
+    chunk: Optional[int] = None
+    unit_norm_eps: Optional[float] = None
+    own_kv: bool = True
 
 
 @dataclass(frozen=True)
@@ -123,11 +148,49 @@ class FeedForwardSpec:
 
 @dataclass(frozen=True)
 class GatedMLPSpec(FeedForwardSpec):
-    """Dense gated feed-forward: down(act(gate(x)) * up(x))."""
+    """Dense gated feed-forward: down(act(gate(x)) * up(x)); ``activation`` "silu"
+    or "gelu_tanh".  ``biases``: every one of the three products adds a vector
+    (tensor roles "gate_bias", "up_bias", "down_bias")."""
 
     hidden_size: int = 0
     intermediate_size: int = 0
     activation: str = "silu"
+    biases: bool = False
+
+
+@dataclass(frozen=True)
+class TableExpertsSpec(FeedForwardSpec):
+    """``num_experts`` small gated feed-forwards without biases, of which every
+    token uses ``top``: an integer table [vocab_size, top] (tensor role
+    "expert_table"; the entries of a row differ) names them by the token's id, and
+    the output is the mean of theirs.  Tensor roles of expert e: "expert_gate",
+    "expert_up", "expert_down", each a name with ``{e}`` where the number goes."""
+
+    hidden_size: int = 0
+    intermediate_size: int = 0
+    num_experts: int = 0
+    top: int = 0
+    vocab_size: int = 0
+    activation: str = "silu"
+
+
+@dataclass(frozen=True)
+class TokenInputSpec:
+    """A per-layer input from the token's id at the end of a block.  A table shared
+    by all layers (``table_name`` [vocab_size, table_width]) holds ``dim`` features
+    per layer, this layer's from column ``offset`` on.  With x the residual:
+    g = act(G x) * e[token]; y = P g; x += residual_scale * y / rms(y) * w
+    (tensor roles "token_gate" [dim, hidden], "token_proj" [hidden, dim],
+    "token_norm" [hidden]; ``eps`` inside the root)."""
+
+    hidden_size: int
+    dim: int
+    offset: int
+    table_name: str
+    table_width: int
+    vocab_size: int
+    activation: str
+    eps: float
 
 
 @dataclass(frozen=True)
@@ -161,6 +224,9 @@ class LayerSpec:
     weight_prefix: str
     weight_names: Tuple[Tuple[str, str], ...] = ()
     mixer_conv: Optional[ShortConvSpec] = None
+    # arrangement "parallel": one norm, x += residual_scale * (mixer(norm(x)) + ff(norm(x)))
+    residual_scale: float = 1.0
+    token_input: Optional[TokenInputSpec] = None
 
     def names(self) -> dict:
         return dict(self.weight_names)
@@ -226,3 +292,6 @@ class ModelSpec:
     input_adapters: Tuple[AdapterSpec, ...] = ()      # run on the residual right after the embedding
     logit_adapters: Tuple[AdapterSpec, ...] = ()      # run on the 32-bit logits of the wanted rows
     stream_adapters: Tuple[AdapterSpec, ...] = ()     # run on the residual where a run step's ``enter`` names them
+    # tensors that several parts read and none owns: (name, shape, "float" | "int"); every part finds
+    # them in the dict it is bound with
+    shared_tensors: Tuple[Tuple[str, Tuple[int, ...], str], ...] = ()

@@ -11,7 +11,9 @@
 // the batch around it.
 //
 // Query token i of sequence s sits at position ctx_len[s] - q_len[s] + i and
-// sees keys max(0, pos - window + 1) .. pos (window 0 = all).
+// sees keys max(0, pos - window + 1) .. pos (window 0 = all); with chunk > 0 only those of its own
+// block of `chunk` positions, counted from the sequence's start.  Keys have d features, values dv
+// (the two caches are [pages, kv heads, page, d] and [.., dv]; the output rows have nq * dv).
 //
 // Options of the score: a soft cap c (0 = off) replaces s by c * tanh(s / c); a bias by
 // distance (r1, r2 per query head, null = off) then takes r1 * ln(1 + r2 * (pos - key)) off.
@@ -31,8 +33,8 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cach
                          const int* __restrict__ q_start, const int* __restrict__ ctx_len,
                          const int* __restrict__ seq_of_token, const int* __restrict__ seq_rows,
                          const int* __restrict__ positions,
-                         long long tokens, int nq, int nkv, int d, int page_size, int num_pages,
-                         float scale, int window, float softcap, const float* __restrict__ bias_r1,
+                         long long tokens, int nq, int nkv, int d, int dv, int page_size, int num_pages,
+                         float scale, int window, int chunk, float softcap, const float* __restrict__ bias_r1,
                          const float* __restrict__ bias_r2, int* __restrict__ error)
 {
     pdl_enter();
@@ -52,7 +54,7 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cach
         qs[j] = to_f32(qrow[j]);
     __syncwarp();
 
-    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int first = first_visible_key(pos, window, chunk);
     const float r1 = bias_r1 ? bias_r1[head] : 0.f, r2 = bias_r1 ? bias_r2[head] : 0.f;
     const int* table = block_table + (size_t)(seq_rows ? seq_rows[seq] : seq) * table_stride;
     constexpr int SLOTS = MAX_D / 32;
@@ -72,8 +74,8 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cach
                 if (error)
                     atomicExch(error, 3);
             } else {
-                row_off = (((long long)page * nkv + kv_head) * page_size + (u % page_size)) * d;
-                const TC* krow = k_cache + row_off;
+                row_off = ((long long)page * nkv + kv_head) * page_size + (u % page_size);
+                const TC* krow = k_cache + row_off * d;
                 float dot = 0.f;
                 for (int j = 0; j < d; ++j)
                     dot = fmaf(qs[j], to_f32(krow[j]), dot);
@@ -99,21 +101,21 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cach
             const long long off = __shfl_sync(0xffffffffu, row_off, kk);
             if (off < 0)
                 continue;
-            const TC* vrow = v_cache + off;
+            const TC* vrow = v_cache + off * dv;
 #pragma unroll
             for (int i = 0; i < SLOTS; ++i) {
                 const int j = lane + 32 * i;
-                if (j < d)
+                if (j < dv)
                     acc[i] = fmaf(pk, to_f32(vrow[j]), acc[i]);
             }
         }
     }
-    TQ* orow = out + ((size_t)t * nq + head) * d;
+    TQ* orow = out + ((size_t)t * nq + head) * dv;
     const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
     for (int i = 0; i < SLOTS; ++i) {
         const int j = lane + 32 * i;
-        if (j < d)
+        if (j < dv)
             orow[j] = from_f32<TQ>(acc[i] * inv);
     }
 }
@@ -128,14 +130,14 @@ CHIBI_API int chibi_attention_generic(const void* q, int q_type, const void* k_c
                                       const int* q_start, const int* ctx_len,
                                       const int* seq_of_token, const int* seq_rows,
                                       const int* positions,
-                                      long long tokens, int nq, int nkv, int d, int page_size,
-                                      int num_pages, float scale, int window, float softcap,
+                                      long long tokens, int nq, int nkv, int d, int dv, int page_size,
+                                      int num_pages, float scale, int window, int chunk, float softcap,
                                       const float* bias_r1, const float* bias_r2, int* error,
                                       cudaStream_t stream)
 {
     if (tokens <= 0)
         return CHIBI_OK;
-    if (d <= 0 || d > MAX_D || nkv <= 0 || nq % nkv != 0 || window < 0 || softcap < 0.f || (bias_r1 != nullptr) != (bias_r2 != nullptr))
+    if (d <= 0 || d > MAX_D || dv <= 0 || dv > MAX_D || nkv <= 0 || nq % nkv != 0 || window < 0 || chunk < 0 || softcap < 0.f || (bias_r1 != nullptr) != (bias_r2 != nullptr))
         return CHIBI_ERR_UNSUPPORTED;
     const int warps = 4;
     const long long jobs = tokens * nq;
@@ -146,8 +148,8 @@ CHIBI_API int chibi_attention_generic(const void* q, int q_type, const void* k_c
     CHIBI_DISPATCH_TYPE(q_type, TQ, CHIBI_DISPATCH_TYPE(cache_type, TC, {
         launch(attention_generic_kernel<TQ, TC>, dim3((unsigned)blocks), dim3(warps * 32), smem, stream, 
             (const TQ*)q, (const TC*)k_cache, (const TC*)v_cache, (TQ*)out, block_table,
-            table_stride, q_start, ctx_len, seq_of_token, seq_rows, positions, tokens, nq, nkv, d, page_size,
-            num_pages, scale, window, softcap, bias_r1, bias_r2, error);
+            table_stride, q_start, ctx_len, seq_of_token, seq_rows, positions, tokens, nq, nkv, d, dv, page_size,
+            num_pages, scale, window, chunk, softcap, bias_r1, bias_r2, error);
     }));
     return launch_status();
 }

@@ -52,6 +52,7 @@ struct AttnParams {
     int page_size, num_pages;
     float scale_log2;              // scale * log2(e)
     int window;
+    int chunk;                     // 0: none; else a row sees only keys of its own block of this many positions
     int splits;                    // decode: key ranges per sequence
     float* scratch_o;              // decode: [S, nq, splits, D]
     float* scratch_ml;             // decode: [S, nq, splits, 2]
@@ -445,7 +446,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
         return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pos = p.ctx_len[seq] - 1;
-    const int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int first = first_visible_key(pos, p.window, p.chunk);
     const int key_end = pos + 1;
     const int tiles_total = (key_end - first + DEC_TILE - 1) / DEC_TILE;
     const int tiles_per_split = (tiles_total + p.splits - 1) / p.splits;
@@ -709,7 +710,7 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, PRE_Q_ALIASED ? 3 : 1) attn_pr
 
     const int last_row = min(rows_total, row0 + PRE_ROWS) - 1;
     const int min_pos = pos0 + row0 / p.group, max_pos = pos0 + last_row / p.group;
-    const int key_begin = (p.window > 0 && min_pos - p.window + 1 > 0) ? min_pos - p.window + 1 : 0;
+    const int key_begin = first_visible_key(min_pos, p.window, p.chunk);
     const int key_end = max_pos + 1;
     const int n_tiles = (key_end - key_begin + PRE_KEYS - 1) / PRE_KEYS;
 
@@ -717,8 +718,8 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, PRE_Q_ALIASED ? 3 : 1) attn_pr
     const int r_lo = row0 + warp * 16 + g, r_hi = r_lo + 8;
     const int pos_lo = r_lo < rows_total ? pos0 + r_lo / p.group : -1;
     const int pos_hi = r_hi < rows_total ? pos0 + r_hi / p.group : -1;
-    const int first_lo = (p.window > 0 && pos_lo - p.window + 1 > 0) ? pos_lo - p.window + 1 : 0;
-    const int first_hi = (p.window > 0 && pos_hi - p.window + 1 > 0) ? pos_hi - p.window + 1 : 0;
+    const int first_lo = first_visible_key(pos_lo, p.window, p.chunk);
+    const int first_hi = first_visible_key(pos_hi, p.window, p.chunk);
     const ScoreOptions opt = score_options(p, r_lo < rows_total ? kv_head * p.group + r_lo % p.group : -1,
                                            r_hi < rows_total ? kv_head * p.group + r_hi % p.group : -1);
     // rows of this warp: positions between warp_min_pos and warp_max_pos
@@ -727,8 +728,7 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, PRE_Q_ALIASED ? 3 : 1) attn_pr
     const bool warp_active = w_first_row < rows_total;
     const int warp_max_pos = warp_active ? pos0 + w_last_row / p.group : -1;
     const int warp_min_first = !warp_active ? 0
-        : ((p.window > 0 && pos0 + w_first_row / p.group - p.window + 1 > 0)
-               ? pos0 + w_first_row / p.group - p.window + 1 : 0);
+        : (first_visible_key(pos0 + w_first_row / p.group, p.window, p.chunk));
 
     auto issue = [&](int i) {
         if (i < n_tiles) {
@@ -811,13 +811,13 @@ CHIBI_API long long chibi_attention_mma_scratch_floats(int seqs, int nq, int spl
 CHIBI_API int chibi_attention_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
                                   const int* block_table, int table_stride, const int* seq_rows,
                                   const int* q_start, const int* ctx_len, int seqs, int nq, int nkv, int page_size,
-                                  int num_pages, float scale, int window, int mode, int max_q_len,
+                                  int num_pages, float scale, int window, int chunk, int mode, int max_q_len,
                                   int splits, float* scratch, long long scratch_floats, float softcap,
                                   const float* bias_r1, const float* bias_r2, int* error, cudaStream_t stream)
 {
     if (seqs <= 0)
         return CHIBI_OK;
-    if (nkv <= 0 || nq % nkv != 0 || window < 0 || page_size <= 0 || splits < 1 || softcap < 0.f
+    if (nkv <= 0 || nq % nkv != 0 || window < 0 || chunk < 0 || page_size <= 0 || splits < 1 || softcap < 0.f
         || (bias_r1 != nullptr) != (bias_r2 != nullptr))
         return CHIBI_ERR_ARGUMENT;
     AttnParams p {};
@@ -837,6 +837,7 @@ CHIBI_API int chibi_attention_mma(const void* q, const void* k_cache, const void
     p.num_pages = num_pages;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.window = window;
+    p.chunk = chunk;
     p.splits = splits;
     p.error = error;
     p.skip_single = (mode & 1) ? 1 : 0;
@@ -895,14 +896,14 @@ CHIBI_API int chibi_attention_decode_fused(const float* partial, int partial_spl
                                            long long tokens, void* k_cache, void* v_cache, void* out,
                                            const int* block_table, int table_stride, const int* seq_rows,
                                            const int* q_start, const int* ctx_len, int seqs, int nq, int nkv,
-                                           int page_size, int num_pages, float scale, int window, int splits,
+                                           int page_size, int num_pages, float scale, int window, int chunk, int splits,
                                            float* scratch, long long scratch_floats, const void* q_norm_w,
                                            const void* k_norm_w, const float* inv_freq, float eps, float offset,
                                            int append, int* error, cudaStream_t stream)
 {
     if (seqs <= 0)
         return CHIBI_OK;
-    if (nkv <= 0 || nq % nkv != 0 || window < 0 || page_size <= 0 || splits < 1 || !partial || partial_splits < 1
+    if (nkv <= 0 || nq % nkv != 0 || window < 0 || chunk < 0 || page_size <= 0 || splits < 1 || !partial || partial_splits < 1
         || !inv_freq)
         return CHIBI_ERR_ARGUMENT;
     if (D != 128 || nq / nkv > 6 || partial_width < (long long)(append ? nq + 2 * nkv : nq) * D)
@@ -925,6 +926,7 @@ CHIBI_API int chibi_attention_decode_fused(const float* partial, int partial_spl
     p.num_pages = num_pages;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.window = window;
+    p.chunk = chunk;
     p.splits = splits;
     p.error = error;
     p.skip_single = 1;

@@ -62,6 +62,7 @@ struct AttnTcParams {
     int num_pages;
     float scale_log2;
     int window;
+    int chunk;                     // 0: none; else a row sees only keys of its own block of this many positions
     int skip_single;
     int* error;
     // Options of the score (the kernel with one query tile per CTA only): a soft cap c replaces a
@@ -150,7 +151,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
     const int last_row = min(rows_total, row0 + ROWS) - 1;
     const int min_pos = pos0 + row0 / p.group, max_pos = pos0 + last_row / p.group;
-    int key_begin = (p.window > 0 && min_pos - p.window + 1 > 0) ? min_pos - p.window + 1 : 0;
+    int key_begin = first_visible_key(min_pos, p.window, p.chunk);
     key_begin = key_begin / p.page_size * p.page_size;           // tiles start on a page
     const int key_end = max_pos + 1;
     int n_tiles = (key_end - key_begin + KEYS - 1) / KEYS;
@@ -305,7 +306,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const bool live = r < rows_total;
         const int tok = live ? r / p.group : 0;
         const int pos = live ? pos0 + tok : -1;
-        const int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+        const int first = first_visible_key(pos, p.window, p.chunk);
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         // with options the scores are brought to their final form (in units of log2) right after
         // they are read, and the scale below is 1
@@ -594,7 +595,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     // key tiles: all start at key_begin (a page boundary at or before the first key that the
     // CTA's first row sees); tile q needs nt[q] of them, nt[0] <= nt[1] when tile 1 has rows
     const int min_pos = pos0 + row0 / p.group;
-    int key_begin = (p.window > 0 && min_pos - p.window + 1 > 0) ? min_pos - p.window + 1 : 0;
+    int key_begin = first_visible_key(min_pos, p.window, p.chunk);
     key_begin = key_begin / p.page_size * p.page_size;
     int nt[2], key_end = 0;
 #pragma unroll
@@ -758,7 +759,7 @@ attn_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         const bool live = r < rows_total;
         const int tok = live ? r / p.group : 0;
         const int pos = live ? pos0 + tok : -1;
-        const int first = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+        const int first = first_visible_key(pos, p.window, p.chunk);
         const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
         const uint32_t s_addr = lane_addr + q * 128;
         const uint32_t o_addr = lane_addr + 256 + q * 128;
@@ -938,7 +939,7 @@ CHIBI_API int chibi_attention_tc_head_dim() { return D; }
 CHIBI_API int chibi_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out,
                                          const int* block_table, int table_stride, const int* seq_rows,
                                          const int* q_start, const int* ctx_len, int seqs, int nq, int nkv,
-                                         int page_size, int num_pages, float scale, int window,
+                                         int page_size, int num_pages, float scale, int window, int chunk,
                                          int skip_single, int max_q_len, int variant, int kv_splits,
                                          float* scratch, long long scratch_floats, long long tokens,
                                          float softcap, const float* bias_r1, const float* bias_r2,
@@ -946,7 +947,7 @@ CHIBI_API int chibi_attention_prefill_tc(const void* q, const void* k_cache, con
 {
     if (seqs <= 0)
         return CHIBI_OK;
-    if (nkv <= 0 || nq % nkv != 0 || window < 0 || variant < 0 || variant > 2 || softcap < 0.f
+    if (nkv <= 0 || nq % nkv != 0 || window < 0 || chunk < 0 || variant < 0 || variant > 2 || softcap < 0.f
         || (bias_r1 != nullptr) != (bias_r2 != nullptr))
         return CHIBI_ERR_ARGUMENT;
 
@@ -970,6 +971,7 @@ CHIBI_API int chibi_attention_prefill_tc(const void* q, const void* k_cache, con
     p.cache_rows = (long long)num_pages * nkv * page_size;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.window = window;
+    p.chunk = chunk;
     p.skip_single = skip_single;
     p.error = error;
     p.kv_splits = 1;

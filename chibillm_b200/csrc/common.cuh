@@ -21,6 +21,20 @@
 
 namespace chibi {
 
+// The oldest key that the query at position `pos` sees.  A window of W positions (0: none) gives
+// pos - W + 1; blocks of C positions counted from the sequence's start (0: none) give the start of
+// pos's own block; both together the later of the two; never below 0.  It does not fall as pos grows,
+// so the value of a tile's first row bounds the tile.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int window, int chunk)
+{
+    int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (chunk > 0 && pos > 0) {
+        const int start = pos - pos % chunk;
+        first = start > first ? start : first;
+    }
+    return first;
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -52,6 +52,7 @@ class DecoderModel:
             out += b.expected_tensors()
         for a in self.input_adapters + self.logit_adapters + self.stream_adapters:
             out += a.expected_tensors()
+        out += [TensorSpec(name, tuple(shape), kind) for name, shape, kind in s.shared_tensors]
         return out
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:

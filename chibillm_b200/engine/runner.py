@@ -50,7 +50,9 @@ def make_runtime(dtype, device="cuda:0", kernels=None, spec=None) -> Runtime:
         from ..kernels.ops import CudaKernels
         if spec is not None:
             from ..csrc import build
-            head_dims = {layer.mixer.head_dim for layer in spec.layers if layer.mixer.kind == "attention"}
+            # (value heads of a size of their own run the plain attention kernel: no library to build)
+            head_dims = {layer.mixer.head_dim for layer in spec.layers if layer.mixer.kind == "attention"
+                         and getattr(layer.mixer, "value_dim", None) in (None, layer.mixer.head_dim)}
             build.prepare(head_dims, bfloat16=parse_dtype(dtype) == torch.bfloat16)
         kernels = CudaKernels(device)
     return Runtime(device=device, dtype=parse_dtype(dtype), kernels=kernels)

@@ -45,7 +45,7 @@ _SIGNATURES = {
         "chibi_reduce_swiglu": [P, I, I, I, P, I, I, P],
         "chibi_qk_norm_rope_append_partial": [P, I, L, L, P, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I,
                                               I, I, F, F, I, P, P],
-        "chibi_attention_generic": [P, I, P, P, I, P, P, I, P, P, P, P, P, L, I, I, I, I, I, F, I, F, P, P, P, P],
+        "chibi_attention_generic": [P, I, P, P, I, P, P, I, P, P, P, P, P, L, I, I, I, I, I, I, F, I, I, F, P, P, P, P],
         "chibi_short_conv": [P, I, L, P, P, P, P, L, P, P, I, I, I, I, P],
         "chibi_delta_rule": [P, I, L, P, P, P, P, P, P, P, I, I, I, I, I, F, F, P],
         "chibi_decay_logits": [P, I, L, P, P, L, I, I, P],
@@ -56,15 +56,25 @@ _SIGNATURES = {
         "chibi_activation": [P, I, L, I, P],
         "chibi_reduce_activation": [P, I, L, P, I, I, P],
         "chibi_sample": [P, L, L, I, P, P, P, P, L, P],
+        "chibi_heads_rotate_append": [P, I, L, P, P, P, I, P, F, P, P, P, P, I, L, I, I, I, I, I, I, I, F, I, I, P, P],
+        "chibi_gated_activation": [P, I, L, P, I, P, L, I, I, P],
+        "chibi_route_by_table": [P, P, I, I, I, L, P, P, P],
+        "chibi_expert_rows_gemm": [P, I, L, I, I, P, I, P, L, P, L, I, I, I, I, I, P],
+        "chibi_combine_experts": [P, P, P, L, L, I, I, I, F, P],
+        "chibi_layer_end": [P, P, F, P, P, L, I, I, P, P, P, P, I, I, F, P, F, P, I, I, L, I, P, P],
+        "chibi_side_gate": [P, I, L, P, P, I, L, I, I, L, I, I, P, P],
+        "chibi_softcap": [P, F, L, P],
+        "chibi_zero": [P, L, P],
+        "chibi_expert_tile_rows": [],
     },
     "chibi_attention_tc": {
         "chibi_attention_tc_head_dim": [],
-        "chibi_attention_prefill_tc": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, P, L, L, F, P, P, P, P],
+        "chibi_attention_prefill_tc": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, I, P, L, L, F, P, P, P, P],
     },
     "chibi_attention_mma": {
         "chibi_attention_mma_head_dim": [],
-        "chibi_attention_mma": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, P, L, F, P, P, P, P],
-        "chibi_attention_decode_fused": [P, I, L, L, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, P, L, P, P, P,
+        "chibi_attention_mma": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, P, L, F, P, P, P, P],
+        "chibi_attention_decode_fused": [P, I, L, L, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, P, L, P, P, P,
                                          F, F, I, P, P],
     },
 }

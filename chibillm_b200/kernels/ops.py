@@ -440,6 +440,7 @@ class CudaKernels:
             what = {1: "a token id outside the vocabulary", 2: "a page id outside the pool (append)",
                     3: "a page id outside the pool (attention)",
                     4: "a block-table update outside the table",
+                    5: "a table entry outside its range (an expert, or a token id of a per-layer token input)",
                     11: "a wait that ran out (matrix product: loader)",
                     12: "a wait that ran out (matrix product: tensor-core issuer)",
                     13: "a wait that ran out (matrix product: epilogue)",
@@ -748,14 +749,18 @@ class CudaKernels:
                   nq: int, nkv: int, d: int, page_size: int, scale: float,
                   window: Optional[int], max_q_len: int, max_ctx_len: int, min_q_len: int = 0,
                   seq_rows: Optional[torch.Tensor] = None, softcap: Optional[float] = None,
-                  distance_bias=None) -> None:
+                  distance_bias=None, chunk: Optional[int] = None, value_dim: Optional[int] = None) -> None:
         """Causal attention of every token over its sequence's pages.  bfloat16
         with a head size that is a multiple of 16 runs on the tensor cores (one
         library per head size, compiled when first needed); everything else, the
         32-bit path included, runs the plain kernel.  ``softcap`` c: a scaled score
         s becomes c * tanh(s / c).  ``distance_bias`` (r1, r2), float32 [nq] each:
         r1[h] * ln(1 + r2[h] * (i - j)) is taken off the score of query i and key j.
-        ``v_cache`` may be ``k_cache`` itself (values tied to the keys)."""
+        ``v_cache`` may be ``k_cache`` itself (values tied to the keys).  ``chunk`` C: a
+        query sees only the keys of its own block of C positions, counted from the
+        sequence's start.  ``value_dim``: the size of a value head where it is not d
+        (the value cache is [pages, nkv, page, value_dim], out [T, nq * value_dim]);
+        such a layer runs the plain kernel."""
         _need_cuda(q, k_cache, v_cache, out, block_table, q_start, ctx_len, seq_of_token, positions,
                    seq_rows)
         r1 = r2 = None
@@ -769,26 +774,33 @@ class CudaKernels:
         if cap < 0.0:
             raise KernelError("attention: the soft cap must be positive")
         T = q.shape[0]
-        if not q.is_contiguous() or not out.is_contiguous() or q.shape != (T, nq * d) or out.shape != q.shape:
-            raise KernelError("attention: q / out must be contiguous [T, nq*d]")
+        dv = d if value_dim is None else int(value_dim)
+        chunk = int(chunk or 0)
+        if chunk < 0:
+            raise KernelError("attention: the chunk size must be positive")
+        if not q.is_contiguous() or not out.is_contiguous() or q.shape != (T, nq * d) or out.shape != (T, nq * dv):
+            raise KernelError("attention: q must be contiguous [T, nq*d] and out [T, nq*value_dim]")
         if out.dtype != q.dtype:
             raise KernelError("attention: out must have q's element type")
-        if (k_cache.shape != v_cache.shape or k_cache.dim() != 4 or not k_cache.is_contiguous()
-                or not v_cache.is_contiguous() or tuple(k_cache.shape[1:]) != (nkv, page_size, d)):
-            raise KernelError(f"attention: cache shape {tuple(k_cache.shape)}")
+        if (k_cache.dim() != 4 or v_cache.dim() != 4 or not k_cache.is_contiguous()
+                or not v_cache.is_contiguous() or tuple(k_cache.shape[1:]) != (nkv, page_size, d)
+                or tuple(v_cache.shape) != (k_cache.shape[0], nkv, page_size, dv)):
+            raise KernelError(f"attention: cache shapes {tuple(k_cache.shape)} / {tuple(v_cache.shape)}")
         _rows_contiguous(block_table, "attention: block_table")
         if (self.use_tensor_cores and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
-                and d % 16 == 0 and d <= 256):
+                and d % 16 == 0 and d <= 256 and dv == d):
             self._attention_mma(q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d,
-                                page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows, cap, r1, r2)
+                                page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows, cap, r1, r2,
+                                chunk)
             return
         self.launches += 1
         _check(self.lib.chibi_attention_generic(
             _ptr(q), _code(q), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(out),
             _ptr(block_table), block_table.stride(0), _ptr(q_start), _ptr(ctx_len),
-            _ptr(seq_of_token), _ptr(seq_rows), _ptr(positions), T, nq, nkv, d, page_size,
+            _ptr(seq_of_token), _ptr(seq_rows), _ptr(positions), T, nq, nkv, d, dv, page_size,
             k_cache.shape[0],
-            float(scale), int(window or 0), cap, _ptr(r1), _ptr(r2), _ptr(self.error), self._stream()), "attention")
+            float(scale), int(window or 0), chunk, cap, _ptr(r1), _ptr(r2), _ptr(self.error), self._stream()),
+            "attention")
 
     def decode_attention_splits(self, seqs: int, nq: int, nkv: int, max_ctx_len: int) -> int:
         """Key ranges per sequence of the decode attention kernel: as many CTAs as
@@ -832,7 +844,7 @@ class CudaKernels:
 
     def _attention_mma(self, q, k_cache, v_cache, out, block_table, q_start, ctx_len, nq, nkv, d,
                        page_size, scale, window, max_q_len, max_ctx_len, min_q_len, seq_rows,
-                       softcap: float = 0.0, bias_r1=None, bias_r2=None) -> None:
+                       softcap: float = 0.0, bias_r1=None, bias_r2=None, chunk: int = 0) -> None:
         lib = self._attention_libs.get(d)
         if lib is None:
             lib = self._load("chibi_attention_mma", (f"CHIBI_HEAD_DIM={d}",))
@@ -855,7 +867,7 @@ class CudaKernels:
             status = tc.chibi_attention_prefill_tc(
                 _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
                 _ptr(seq_rows), _ptr(q_start), _ptr(ctx_len), seqs, nq, nkv, page_size, k_cache.shape[0],
-                float(scale), int(window or 0), 1 if mode & 1 else 0, int(max_q_len),
+                float(scale), int(window or 0), int(chunk), 1 if mode & 1 else 0, int(max_q_len),
                 int(self.tcgen05_attention_variant), kv_splits, _ptr(part),
                 part.numel() if part is not None else 0, q.shape[0], float(softcap), _ptr(bias_r1), _ptr(bias_r2),
                 _ptr(self.error), self._stream())
@@ -875,7 +887,7 @@ class CudaKernels:
         status = lib.chibi_attention_mma(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), block_table.stride(0),
             _ptr(seq_rows), _ptr(q_start), _ptr(ctx_len), seqs, nq, nkv, page_size, k_cache.shape[0], float(scale),
-            int(window or 0), mode, int(max_q_len), splits, _ptr(scratch),
+            int(window or 0), int(chunk), mode, int(max_q_len), splits, _ptr(scratch),
             scratch.numel() if scratch is not None else 0, float(softcap), _ptr(bias_r1), _ptr(bias_r2),
             _ptr(self.error), self._stream())
         self.launches += (1 if mode & 1 else 0) + (1 if mode & 1 and splits > 1 else 0) + (1 if mode & 2 else 0)
@@ -923,7 +935,7 @@ class CudaKernels:
         status = lib.chibi_attention_decode_fused(
             _ptr(pending.partial), pending.splits, width, seqs, _ptr(k_cache), _ptr(v_cache), _ptr(out),
             _ptr(block_table), block_table.stride(0), _ptr(seq_rows), _ptr(q_start), _ptr(ctx_len), seqs, nq, nkv,
-            page_size, k_cache.shape[0], float(scale), int(window or 0), splits, _ptr(scratch),
+            page_size, k_cache.shape[0], float(scale), int(window or 0), 0, splits, _ptr(scratch),
             scratch.numel() if scratch is not None else 0, _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
             float(eps), float(norm_offset), 1 if append else 0, _ptr(self.error), self._stream())
         if status == -2:
@@ -1122,6 +1134,173 @@ class CudaKernels:
                                                 _ptr(out), _code(out), self.ACTIVATIONS[kind], self._stream()),
                "reduce_activation")
         return True
+
+    # ---- parts of layer_ops.cu
+    def heads_rotate_append(self, qkv: torch.Tensor, q_out: torch.Tensor, k_cache: Optional[torch.Tensor],
+                            v_cache: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], rotary_dim: int,
+                            amplitude: float, unit_norm: bool, eps: float, positions: torch.Tensor,
+                            seq_of_token: torch.Tensor, block_table: Optional[torch.Tensor], nq: int, nkv: int,
+                            d: int, dv: int, page_size: int, seq_rows: Optional[torch.Tensor] = None) -> None:
+        """Per head of a row q | k | v ([T, nq d + nkv d + nkv dv]; [T, nq d] without a
+        cache): rotation of the first ``rotary_dim`` features (cosines and sines times
+        ``amplitude``), then, with ``unit_norm``, the head divided by its root mean
+        square; q -> q_out, k and v -> cache pages ([pages, nkv, page, d] and [.., dv])."""
+        _need_cuda(qkv, q_out, k_cache, v_cache, inv_freq, positions, seq_of_token, block_table, seq_rows)
+        _rows_contiguous(qkv, "heads_rotate_append: qkv")
+        T = qkv.shape[0]
+        append = k_cache is not None
+        width = nq * d + (nkv * (d + dv) if append else 0)
+        if qkv.shape[1] < width or not q_out.is_contiguous() or q_out.shape != (T, nq * d) or q_out.dtype != qkv.dtype:
+            raise KernelError("heads_rotate_append: qkv / q_out shapes or types")
+        if rotary_dim and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() < rotary_dim // 2):
+            raise KernelError("heads_rotate_append: inv_freq must hold rotary_dim/2 float32 values")
+        num_pages = table_stride = 0
+        if append:
+            if (v_cache is None or not k_cache.is_contiguous() or not v_cache.is_contiguous()
+                    or tuple(k_cache.shape[1:]) != (nkv, page_size, d)
+                    or tuple(v_cache.shape) != (k_cache.shape[0], nkv, page_size, dv) or v_cache.dtype != k_cache.dtype):
+                raise KernelError(f"heads_rotate_append: cache shapes {tuple(k_cache.shape)}")
+            num_pages = k_cache.shape[0]
+            _rows_contiguous(block_table, "heads_rotate_append: block_table")
+            table_stride = block_table.stride(0)
+        self.launches += 1
+        _check(self.lib.chibi_heads_rotate_append(
+            _ptr(qkv), _code(qkv), qkv.stride(0), _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+            _code(k_cache) if append else F32, _ptr(inv_freq), float(amplitude), _ptr(positions), _ptr(seq_of_token),
+            _ptr(seq_rows), _ptr(block_table), table_stride, T, nq, nkv, d, dv, int(rotary_dim), page_size, num_pages,
+            float(eps), 1 if unit_norm else 0, 1 if append else 0, _ptr(self.error), self._stream()),
+            "heads_rotate_append")
+
+    def gated_activation(self, gate_up: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                         kind: str) -> None:
+        """out = act(gate + b_gate) * (up + b_up); gate_up [T, 2 n] (gate columns first),
+        bias [2 n] or None."""
+        _need_cuda(gate_up, bias, out)
+        _rows_contiguous(gate_up, "gated_activation: gate_up")
+        T, n = out.shape
+        if gate_up.shape != (T, 2 * n) or not out.is_contiguous() or out.dtype != gate_up.dtype \
+                or kind not in self.ACTIVATIONS or (bias is not None and (bias.shape != (2 * n,)
+                                                                          or not bias.is_contiguous())):
+            raise KernelError("gated_activation: shapes, types or activation")
+        self.launches += 1
+        _check(self.lib.chibi_gated_activation(_ptr(gate_up), _code(gate_up), gate_up.stride(0), _ptr(bias),
+                                               _code(bias) if bias is not None else F32, _ptr(out), T, n,
+                                               self.ACTIVATIONS[kind], self._stream()), "gated_activation")
+
+    def route_words(self, pairs: int, experts: int) -> int:
+        """int32 values of the routing scratch for ``pairs`` (token, choice) pairs."""
+        tile = int(self.lib.chibi_expert_tile_rows())
+        return (experts + 1) + 2 * pairs + 2 * ((pairs + tile - 1) // tile + experts)
+
+    def routed_experts(self, x: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, gate_up: torch.Tensor,
+                       down: torch.Tensor, acc: torch.Tensor, route: torch.Tensor, act: torch.Tensor,
+                       y: torch.Tensor, kind: str, weight: float) -> None:
+        """acc[t] += weight * sum over the experts that ``table[tokens[t]]`` names (in the
+        table's order) of down_e (act(gate_e x[t]) * (up_e x[t])).  gate_up [E, 2 F, D]
+        (gate rows first), down [E, D, F], table int32 [vocab, top]; scratch: route int32
+        (``route_words``), act [T top, F] in x's type, y float32 [T top, D].  Four
+        launches; nothing is read on the host."""
+        _need_cuda(x, tokens, table, gate_up, down, acc, route, act, y)
+        _rows_contiguous(x, "routed_experts: x")
+        _rows_contiguous(acc, "routed_experts: acc")
+        T, D = x.shape
+        E, F2, _ = gate_up.shape
+        F = F2 // 2
+        vocab, top = table.shape
+        pairs = T * top
+        if (gate_up.shape != (E, 2 * F, D) or down.shape != (E, D, F) or not gate_up.is_contiguous()
+                or not down.is_contiguous() or down.dtype != gate_up.dtype or table.dtype != torch.int32
+                or not table.is_contiguous() or tokens.dtype != torch.int32 or acc.dtype != torch.float32
+                or acc.shape != (T, D) or route.dtype != torch.int32 or route.numel() < self.route_words(pairs, E)
+                or act.shape != (pairs, F) or act.dtype != x.dtype or not act.is_contiguous()
+                or y.shape != (pairs, D) or y.dtype != torch.float32 or not y.is_contiguous()
+                or kind not in self.ACTIVATIONS):
+            raise KernelError("routed_experts: shapes or types")
+        stream = self._stream()
+        self.launches += 4
+        _check(self.lib.chibi_route_by_table(_ptr(tokens), _ptr(table), vocab, top, E, T, _ptr(route),
+                                             _ptr(self.error), stream), "routed_experts (route)")
+        _check(self.lib.chibi_expert_rows_gemm(_ptr(x), _code(x), x.stride(0), 1, top, _ptr(gate_up), _code(gate_up),
+                                               _ptr(act), F, _ptr(route), pairs, E, F, D, 1, self.ACTIVATIONS[kind],
+                                               stream), "routed_experts (gate | up)")
+        _check(self.lib.chibi_expert_rows_gemm(_ptr(act), _code(act), F, 0, top, _ptr(down), _code(down), _ptr(y), D,
+                                               _ptr(route), pairs, E, D, F, 0, 0, stream), "routed_experts (down)")
+        _check(self.lib.chibi_combine_experts(_ptr(y), _ptr(route), _ptr(acc), acc.stride(0), T, D, top, E,
+                                              float(weight), stream), "routed_experts (combine)")
+
+    def layer_end(self, residual: torch.Tensor, delta: Optional[torch.Tensor], mult: float, side=None,
+                  y_in: Optional[torch.Tensor] = None, norm=None) -> None:
+        """residual += mult * delta; then the per-layer token input, if ``side`` is
+        given: (tokens, table [vocab, all], offset, gate [s, n], proj [n, s], norm weight
+        [n], activation, eps): y = proj (act(gate x) * table[token, offset:offset + s]),
+        x += mult * y / rms(y) * weight -- the two products are done by the kernel unless
+        ``y_in`` [T, n] float32 brings y; then, if ``norm`` = (weight, eps, offset, out)
+        is given, out = x / rms(x) * (weight + offset).  One launch, a block per token."""
+        _need_cuda(residual, delta, y_in)
+        T, n = residual.shape
+        if residual.dtype != torch.float32 or not residual.is_contiguous() or (
+                delta is not None and (delta.shape != residual.shape or delta.dtype != torch.float32
+                                       or not delta.is_contiguous())):
+            raise KernelError("layer_end: residual and delta are contiguous float32 [T, n]")
+        tokens = table = gate = proj = side_w = None
+        offset = s = vocab = stride = 0
+        kind, eps = 1, 0.0
+        w_type = F32
+        if side is not None:
+            tokens, table, offset, gate, proj, side_w, act, eps = side
+            _need_cuda(tokens, table, gate, proj, side_w)
+            s, vocab, stride = gate.shape[0], table.shape[0], table.stride(0)
+            kind = self.ACTIVATIONS[act]
+            if (gate.shape != (s, n) or proj.shape != (n, s) or side_w.shape != (n,) or offset + s > table.shape[1]
+                    or not (gate.is_contiguous() and proj.is_contiguous() and side_w.is_contiguous())
+                    or table.stride(1) != 1 or len({table.dtype, gate.dtype, proj.dtype, side_w.dtype}) != 1
+                    or tokens.dtype != torch.int32):
+                raise KernelError("layer_end: shapes or types of the token input")
+            w_type = _code(gate)
+            if y_in is not None and (y_in.shape != (T, n) or y_in.dtype != torch.float32 or not y_in.is_contiguous()):
+                raise KernelError("layer_end: y_in is contiguous float32 [T, n]")
+        norm_w = out = None
+        norm_eps = norm_offset = 0.0
+        if norm is not None:
+            norm_w, norm_eps, norm_offset, out = norm
+            _need_cuda(norm_w, out)
+            if norm_w.shape != (n,) or out.shape != (T, n) or not out.is_contiguous() or not norm_w.is_contiguous():
+                raise KernelError("layer_end: shapes of the norm")
+            if side is not None and (norm_w.dtype != gate.dtype or float(norm_eps) != float(eps)):
+                raise KernelError("layer_end: the norm's weight type and eps must be the token input's")
+            w_type, eps = _code(norm_w), norm_eps
+        self.launches += 1
+        _check(self.lib.chibi_layer_end(
+            _ptr(residual), _ptr(delta), float(mult), _ptr(tokens), _ptr(table), stride, int(offset), vocab, _ptr(gate),
+            _ptr(proj), _ptr(side_w), _ptr(y_in), s, kind, float(eps), _ptr(norm_w), float(norm_offset), _ptr(out),
+            _code(out) if out is not None else F32, w_type, T, n, _ptr(self.error), self._stream()), "layer_end")
+
+    def side_gate(self, gate: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, offset: int, kind: str) -> None:
+        """gate[t, j] = act(gate[t, j]) * table[tokens[t], offset + j], in place."""
+        _need_cuda(gate, tokens, table)
+        _rows_contiguous(gate, "side_gate: gate")
+        if table.stride(1) != 1 or offset + gate.shape[1] > table.shape[1] or tokens.dtype != torch.int32:
+            raise KernelError("side_gate: shapes")
+        self.launches += 1
+        _check(self.lib.chibi_side_gate(_ptr(gate), _code(gate), gate.stride(0), _ptr(tokens), _ptr(table),
+                                        _code(table), table.stride(0), int(offset), table.shape[0], gate.shape[0],
+                                        gate.shape[1], self.ACTIVATIONS[kind], _ptr(self.error), self._stream()),
+               "side_gate")
+
+    def softcap(self, x: torch.Tensor, cap: float) -> None:
+        """x = cap * tanh(x / cap), in place (float32)."""
+        _need_cuda(x)
+        if x.dtype != torch.float32 or not x.is_contiguous() or not cap > 0:
+            raise KernelError("softcap: x must be contiguous float32 and the cap positive")
+        self.launches += 1
+        _check(self.lib.chibi_softcap(_ptr(x), float(cap), x.numel(), self._stream()), "softcap")
+
+    def zero(self, x: torch.Tensor) -> None:
+        _need_cuda(x)
+        if x.dtype != torch.float32 or not x.is_contiguous():
+            raise KernelError("zero: x must be contiguous float32")
+        self.launches += 1
+        _check(self.lib.chibi_zero(_ptr(x), x.numel(), self._stream()), "zero")
 
     def gather_rows(self, x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
         _need_cuda(x, rows, out)

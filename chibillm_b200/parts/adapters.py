@@ -3,6 +3,9 @@
 "scale": multiplies its argument by a constant (``params``: "factor"); as an
 input adapter it scales the embeddings, as a logit adapter the logits.
 
+"softcap": replaces x by cap * tanh(x / cap) (``params``: "cap"); as a logit
+adapter it bounds the logits.
+
 "reentry_mix": a stream adapter for a group of layers that runs several times.
 Before each pass the residual x is replaced by W [x; x0] + step[turn], where x0
 is the residual as the input adapters left it, W is [hidden, 2 * hidden] (x's
@@ -29,6 +32,20 @@ class Scale(Adapter):
     def forward(self, x: torch.Tensor, ctx, turn: int = 0) -> None:
         if self.factor != 1.0:
             self.runtime.kernels.scale(x, self.factor)
+
+
+class SoftCap(Adapter):
+    def __init__(self, spec, runtime: Runtime):
+        self.cap = float(spec.constants()["cap"])
+        if not self.cap > 0:
+            raise ValueError("softcap: the cap must be positive")
+        self.runtime = runtime
+
+    def launch_key(self, ctx):
+        return ()
+
+    def forward(self, x: torch.Tensor, ctx, turn: int = 0) -> None:
+        self.runtime.kernels.softcap(x, self.cap)
 
 
 class ReentryMix(Adapter):
@@ -68,4 +85,5 @@ class ReentryMix(Adapter):
 
 
 register_adapter("scale", Scale, replace=True)
+register_adapter("softcap", SoftCap, replace=True)
 register_adapter("reentry_mix", ReentryMix, replace=True)

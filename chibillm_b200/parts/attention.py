@@ -17,6 +17,15 @@ bias by distance taken off the capped score (r1[h] * ln(1 + r2[h] * (i - j)),
 two learned numbers per query head, kept in 32-bit), and values tied to the
 keys (one product gives q | k, the cache holds keys only and the kernels read
 them as values too).
+
+Further options: value heads of another size than query and key heads
+(``value_dim``), attention inside blocks of ``chunk`` positions, a layer without
+key and value projections that only ever reads another run step's cache
+(``own_kv`` False), and a norm of q and k without a weight AFTER the rotation
+(``unit_norm_eps``), also with a rotation whose cosines and sines carry an
+amplitude.  The last two, and a value size of its own, take the plain order of
+kernels: the q | k | v product, one kernel that rotates, normalises and appends,
+attention, the output product.
 """
 from __future__ import annotations
 
@@ -44,16 +53,28 @@ class PagedAttention(Mixer):
         if spec.distance_bias not in (None, "log"):
             raise ValueError(f"distance bias '{spec.distance_bias}' is not supported (None or 'log')")
         self.kv_arrays = 1 if spec.tied_values else 2
+        self.value_dim = spec.head_dim if spec.value_dim is None else spec.value_dim
+        if spec.tied_values and self.value_dim != spec.head_dim:
+            raise ValueError("values tied to the keys have the keys' size")
+        if spec.unit_norm_eps is not None and spec.qk_norm is not None:
+            raise ValueError("a norm of q and k comes either before the rotation (qk_norm) or after it (unit_norm_eps)")
+        # the plain order of kernels (see the module's text)
+        self.rotate_then_norm = (spec.unit_norm_eps is not None or self.value_dim != spec.head_dim
+                                 or getattr(self.position, "amplitude", 1.0) != 1.0)
+        if self.rotate_then_norm and (spec.tied_values or spec.qk_norm is not None):
+            raise ValueError("tied values and a weighted norm before the rotation are not combined with a norm "
+                             "after the rotation, an amplitude or a value size of its own")
 
     # ---- weights
     def expected_tensors(self) -> List[TensorSpec]:
         s = self.spec
         qw, kw = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
-        out = [TensorSpec(self.names["q_proj"], (qw, s.hidden_size)),
-               TensorSpec(self.names["k_proj"], (kw, s.hidden_size))]
-        if not s.tied_values:
-            out.append(TensorSpec(self.names["v_proj"], (kw, s.hidden_size)))
-        out.append(TensorSpec(self.names["o_proj"], (s.hidden_size, qw)))
+        out = [TensorSpec(self.names["q_proj"], (qw, s.hidden_size))]
+        if s.own_kv:
+            out.append(TensorSpec(self.names["k_proj"], (kw, s.hidden_size)))
+            if not s.tied_values:
+                out.append(TensorSpec(self.names["v_proj"], (s.num_kv_heads * self.value_dim, s.hidden_size)))
+        out.append(TensorSpec(self.names["o_proj"], (s.hidden_size, s.num_heads * self.value_dim)))
         if s.distance_bias is not None:
             out += [TensorSpec(self.names["distance_r1"], (s.num_heads,), init=("uniform", 0.0, 2.0)),
                     TensorSpec(self.names["distance_r2"], (s.num_heads,), init=("uniform", 0.1, 0.5))]
@@ -64,6 +85,8 @@ class PagedAttention(Mixer):
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         roles = ("q_proj", "k_proj") if self.spec.tied_values else ("q_proj", "k_proj", "v_proj")
+        if not self.spec.own_kv:
+            roles = ("q_proj",)
         mats = [tensors[self.names[r]] for r in roles]
         self.qkv = torch.cat([m.to(mats[0].dtype) for m in mats], dim=0).contiguous()
         if self.spec.distance_bias is not None:
@@ -80,7 +103,8 @@ class PagedAttention(Mixer):
     def cache_need(self):
         s = self.spec
         return PagedKVNeed(num_kv_heads=s.num_kv_heads, head_dim=s.head_dim, window=s.window,
-                           tied_values=s.tied_values)
+                           tied_values=s.tied_values,
+                           value_dim=self.value_dim if self.value_dim != s.head_dim else None)
 
     def launch_key(self, ctx):
         if self.position.fused_rotation() is None:
@@ -100,8 +124,12 @@ class PagedAttention(Mixer):
         nq, nkv, d = s.num_heads, s.num_kv_heads, s.head_dim
         qw, kw = nq * d, nkv * d
         writes = cache.writes
+        if writes and not s.own_kv:
+            raise ValueError("a layer without key and value projections must read another run step's cache")
+        if self.rotate_then_norm:
+            return self._rotate_norm_attend(x, residual, ctx, cache)
         width = qw + self.kv_arrays * kw if writes else qw
-        modified = s.softcap is not None or s.distance_bias is not None
+        modified = s.softcap is not None or s.distance_bias is not None or s.chunk is not None
         fused = self.position.fused_rotation()
         if fused is not None and fused[0] is not None and self._heads_from_the_product(x, ctx, cache, fused):
             return self._attend(residual, ctx, cache)
@@ -152,6 +180,29 @@ class PagedAttention(Mixer):
             ctx.seq_rows)
         return self._attend(residual, ctx, cache)
 
+    def _rotate_norm_attend(self, x, residual, ctx, cache):
+        """The plain order: q | k | v product; per head rotation (with the encoding's
+        amplitude), then the norm without a weight; append; attention; output product."""
+        s, rt = self.spec, self.runtime
+        k = rt.kernels
+        T = x.shape[0]
+        nq, nkv, d, dv = s.num_heads, s.num_kv_heads, s.head_dim, self.value_dim
+        writes = cache.writes
+        fused = self.position.fused_rotation()
+        if fused is None:
+            raise ValueError("a norm after the rotation needs a rotation that the kernels apply themselves")
+        inv_freq, rotary_dim = fused
+        w = self.qkv if writes else self.qkv[:nq * d]
+        qkv = ctx.workspace.get("attn.qkv", (T, w.shape[0]), rt.dtype)
+        k.linear(x, w, qkv)
+        q = ctx.workspace.get("attn.q", (T, nq * d), rt.dtype)
+        k.heads_rotate_append(qkv, q, cache.keys if writes else None, cache.values if writes else None, inv_freq,
+                              rotary_dim if inv_freq is not None else 0, getattr(self.position, "amplitude", 1.0),
+                              s.unit_norm_eps is not None, s.unit_norm_eps or 0.0, ctx.positions, ctx.seq_of_token,
+                              ctx.tables[cache.group] if writes else None, nq, nkv, d, dv, cache.page_size,
+                              ctx.seq_rows)
+        return self._attend(residual, ctx, cache)
+
     def _attend(self, residual, ctx, cache):
         """Attention over the cache from the step's q, then the output product, left
         for the next norm to add into the residual."""
@@ -160,11 +211,15 @@ class PagedAttention(Mixer):
         nq, nkv, d = s.num_heads, s.num_kv_heads, s.head_dim
         T = ctx.num_tokens
         q = ctx.workspace.get("attn.q", (T, nq * d), rt.dtype)
-        att = ctx.workspace.get("attn.out", (T, nq * d), rt.dtype)
+        att = ctx.workspace.get("attn.out", (T, nq * self.value_dim), rt.dtype)
         extra = {}
         if s.softcap is not None or s.distance_bias is not None:
             extra = {"softcap": s.softcap, "distance_bias": (self.distance_r1, self.distance_r2)
                      if s.distance_bias is not None else None}
+        if s.chunk is not None:
+            extra["chunk"] = s.chunk
+        if self.value_dim != d:
+            extra["value_dim"] = self.value_dim
         k.attention(q, cache.keys, cache.values, att, ctx.tables[cache.group], ctx.q_start, ctx.ctx_len,
                     ctx.seq_of_token, ctx.positions, nq, nkv, d, cache.page_size, s.scale,
                     s.window, ctx.max_q_len, ctx.max_ctx_len, ctx.min_q_len, ctx.seq_rows, **extra)

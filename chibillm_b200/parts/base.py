@@ -49,12 +49,14 @@ class TensorSpec:
 class PagedKVNeed:
     """Keys and values of every position, in pages; ``window`` None = all keys
     stay, an integer = only that many most recent ones are ever read.
-    ``tied_values``: the values are the keys; the pool holds one array."""
+    ``tied_values``: the values are the keys; the pool holds one array.
+    ``value_dim`` (None: ``head_dim``): the size of a value head."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     tied_values: bool = False
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)

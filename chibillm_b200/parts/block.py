@@ -3,7 +3,15 @@ residual += feed_forward(norm(residual)); the residual itself is never
 normalised in place (src/qwen/qwen_layer.cc:124-146).  Two options of the
 layer's spec: a short convolution over time between the first norm and the
 mixer (it keeps its last inputs per request, so the block then has two cache
-needs), and no feed-forward at all."""
+needs), and no feed-forward at all.
+
+"parallel": one norm whose output both branches read,
+residual += scale * (mixer(norm(residual)) + feed_forward(norm(residual))), then an
+optional per-layer token input (parts/token_input.py).  The branches add into a
+32-bit array of their own; one kernel at the layer's end adds it to the residual
+with the scale, applies the token input and, when the next block's norm asks for
+it, writes that norm's output too (the block leaves that kernel pending, as a
+product is left pending by the other arrangement)."""
 from __future__ import annotations
 
 from typing import Dict, List
@@ -13,6 +21,7 @@ import torch
 from .base import (Block, Runtime, TensorSpec, make_feed_forward, make_mixer, make_norm,
                    register_block)
 from .short_conv import ShortConv
+from .token_input import TokenInput
 
 
 class PreNormBlock(Block):
@@ -67,4 +76,89 @@ class PreNormBlock(Block):
         return self.feed_forward.forward(x if normed is None else normed, residual, ctx)
 
 
+class LayerEnd:
+    """What a parallel block leaves pending: the branches' sum, still to be added
+    to the residual with the block's scale, and the token input after it."""
+
+    def __init__(self, block: "ParallelBlock", delta: torch.Tensor, ctx):
+        self.block, self.delta, self.ctx = block, delta, ctx
+
+    def _run(self, residual: torch.Tensor, norm) -> None:
+        b = self.block
+        k = b.runtime.kernels
+        scale = b.layer.residual_scale
+        ti = b.token_input
+        if ti is None:
+            k.layer_end(residual, self.delta, scale, norm=norm)
+            return
+        side = ti.kernel_arguments(self.ctx)
+        if ti.wants_products(residual.shape[0]):
+            # the token input reads the residual after the block's update, so that comes first
+            k.layer_end(residual, self.delta, scale)
+            y = ti.products(residual, self.ctx)
+            k.layer_end(residual, None, scale, side=side, y_in=y, norm=norm)
+        else:
+            k.layer_end(residual, self.delta, scale, side=side, norm=norm)
+
+    def add_into(self, residual: torch.Tensor) -> None:
+        self._run(residual, None)
+
+    def finish_with_norm(self, residual: torch.Tensor, weight: torch.Tensor, eps: float, offset: float,
+                         out: torch.Tensor, scaled_ok: bool):
+        ti = self.block.token_input
+        if ti is not None and (weight.dtype != ti.norm.dtype or float(eps) != float(ti.spec.eps)):
+            self._run(residual, None)
+            self.block.runtime.kernels.rmsnorm(residual, weight, eps, offset, out)
+            return out
+        self._run(residual, (weight, eps, offset, out))
+        return out
+
+
+class ParallelBlock(Block):
+    def __init__(self, layer, runtime: Runtime):
+        if layer.mixer_conv is not None or layer.feed_forward_norm is not None:
+            raise ValueError("the parallel arrangement has one norm and no convolution")
+        self.layer = layer
+        self.runtime = runtime
+        names = {role: layer.weight_prefix + name for role, name in layer.names().items()}
+        self.mixer_norm = make_norm(layer.mixer_norm, names["mixer_norm"], runtime)
+        self.mixer = make_mixer(layer.mixer, names, runtime)
+        self.feed_forward = None if layer.feed_forward is None else make_feed_forward(layer.feed_forward, names, runtime)
+        self.token_input = None if layer.token_input is None else TokenInput(layer.token_input, names, runtime)
+        self._parts = tuple(p for p in (self.mixer_norm, self.mixer, self.feed_forward, self.token_input)
+                            if p is not None)
+
+    def expected_tensors(self) -> List[TensorSpec]:
+        out: List[TensorSpec] = []
+        for p in self._parts:
+            out.extend(p.expected_tensors())
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for p in self._parts:
+            p.bind(tensors)
+
+    def launch_key(self, ctx):
+        keys = [p.launch_key(ctx) for p in (self.mixer, self.feed_forward, self.token_input) if p is not None]
+        return None if any(k is None for k in keys) else tuple(keys)
+
+    def forward(self, residual: torch.Tensor, ctx, cache, pending=None):
+        rt = self.runtime
+        k = rt.kernels
+        x = ctx.workspace.get("block.normed", tuple(residual.shape), rt.dtype)
+        normed = self.mixer_norm.forward_fused(residual, pending, x, False)
+        normed = x if normed is None else normed
+        delta = ctx.workspace.get("block.delta", tuple(residual.shape), torch.float32)
+        k.zero(delta)
+        left = self.mixer.forward(normed, delta, ctx, cache)
+        if left is not None:
+            left.add_into(delta)          # before the feed-forward starts split products of its own
+        if self.feed_forward is not None:
+            left = self.feed_forward.forward(normed, delta, ctx)
+            if left is not None:
+                left.add_into(delta)
+        return LayerEnd(self, delta, ctx)
+
+
 register_block("prenorm", PreNormBlock, replace=True)
+register_block("parallel", ParallelBlock, replace=True)

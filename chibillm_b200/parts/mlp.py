@@ -1,6 +1,15 @@
 """Dense gated feed-forward (SwiGLU): residual += down(silu(gate(x)) * up(x))
 (src/tensor/functions.cc:220-253).  gate and up are stacked into one matrix so
-one product yields both (src/qwen/qwen_weights.cc:13-16)."""
+one product yields both (src/qwen/qwen_weights.cc:13-16).  With another gate
+activation (the tanh form of gelu) or with biases on the three products the
+gate | up product is followed by one kernel that adds the biases, activates
+and multiplies.
+
+"table_experts": small gated feed-forwards without biases, chosen per token
+from a table by the token's id; the output is the mean of the chosen experts'.
+All experts' matrices are stacked, the (token, choice) pairs are sorted by
+expert on the device, and two products over tiles of one expert's rows do the
+work; nothing is read on the host, so a decode step can be captured."""
 from __future__ import annotations
 
 from typing import Dict, List
@@ -12,9 +21,12 @@ from .base import FeedForward, Runtime, TensorSpec, register_feed_forward
 
 class GatedMLP(FeedForward):
     def __init__(self, spec, names: Dict[str, str], runtime: Runtime):
-        if spec.activation != "silu":
+        if spec.activation not in ("silu", "gelu_tanh"):
             raise ValueError(f"activation '{spec.activation}' is not supported by gated_mlp")
         self.spec = spec
+        self.plain_swiglu = spec.activation == "silu" and not spec.biases
+        self.bias_gate_up: torch.Tensor = None
+        self.bias_down: torch.Tensor = None
         self.names = names
         self.runtime = runtime
         self.gate_up: torch.Tensor = None
@@ -23,15 +35,24 @@ class GatedMLP(FeedForward):
 
     def expected_tensors(self) -> List[TensorSpec]:
         s = self.spec
-        return [TensorSpec(self.names["gate_proj"], (s.intermediate_size, s.hidden_size)),
-                TensorSpec(self.names["up_proj"], (s.intermediate_size, s.hidden_size)),
-                TensorSpec(self.names["down_proj"], (s.hidden_size, s.intermediate_size))]
+        out = [TensorSpec(self.names["gate_proj"], (s.intermediate_size, s.hidden_size)),
+               TensorSpec(self.names["up_proj"], (s.intermediate_size, s.hidden_size)),
+               TensorSpec(self.names["down_proj"], (s.hidden_size, s.intermediate_size))]
+        if s.biases:
+            out += [TensorSpec(self.names["gate_bias"], (s.intermediate_size,), init=("normal", 0.0, 0.1)),
+                    TensorSpec(self.names["up_bias"], (s.intermediate_size,), init=("normal", 0.0, 0.1)),
+                    TensorSpec(self.names["down_bias"], (s.hidden_size,), init=("normal", 0.0, 0.1))]
+        return out
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         gate, up = tensors[self.names["gate_proj"]], tensors[self.names["up_proj"]]
         if gate.dtype != up.dtype:
             up = up.to(gate.dtype)
-        interleave = getattr(self.runtime.kernels, "interleave_gate_up", None)
+        if self.spec.biases:
+            self.bias_gate_up = torch.cat([tensors[self.names["gate_bias"]].to(gate.dtype),
+                                           tensors[self.names["up_bias"]].to(gate.dtype)]).contiguous()
+            self.bias_down = tensors[self.names["down_bias"]].float().contiguous()
+        interleave = getattr(self.runtime.kernels, "interleave_gate_up", None) if self.plain_swiglu else None
         self.gate_up_interleaved = interleave(gate, up) if interleave is not None else None
         # one of the two layouts is kept: blocks of 64 gate rows and their 64 up rows for the kernel
         # that applies SwiGLU itself, else gate rows followed by up rows
@@ -48,6 +69,13 @@ class GatedMLP(FeedForward):
         T = x.shape[0]
         inter = self.spec.intermediate_size
         act = ctx.workspace.get("mlp.act", (T, inter), self.runtime.dtype)
+        if not self.plain_swiglu:
+            gate_up = ctx.workspace.get("mlp.gate_up", (T, 2 * inter), self.runtime.dtype)
+            k.linear(x, self.gate_up, gate_up)
+            k.gated_activation(gate_up, self.bias_gate_up, act, self.spec.activation)
+            if self.bias_down is not None:
+                k.add_row_vector(residual, self.bias_down)
+            return k.linear(act, self.down, residual, residual=residual, defer=True)
         if self.gate_up_interleaved is not None:
             if not k.linear_swiglu(x, self.gate_up_interleaved, act):
                 raise RuntimeError("gated_mlp: the fused kernel refused a shape it was prepared for")
@@ -104,5 +132,62 @@ class DenseMLP(FeedForward):
         return k.linear(act, self.down, residual, residual=residual, defer=True)
 
 
+class TableExperts(FeedForward):
+    def __init__(self, spec, names: Dict[str, str], runtime: Runtime):
+        if spec.activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"activation '{spec.activation}' is not supported by table_experts")
+        if not (0 < spec.top <= spec.num_experts):
+            raise ValueError("table_experts: 0 < top <= num_experts is required")
+        self.spec = spec
+        self.names = names
+        self.runtime = runtime
+        self.table: torch.Tensor = None
+        self.gate_up: torch.Tensor = None       # [experts, 2 ff, hidden]: an expert's gate rows, then its up rows
+        self.down: torch.Tensor = None          # [experts, hidden, ff]
+
+    def _name(self, role: str, e: int) -> str:
+        return self.names[role].replace("{e}", str(e))
+
+    def expected_tensors(self) -> List[TensorSpec]:
+        s = self.spec
+        out = [TensorSpec(self.names["expert_table"], (s.vocab_size, s.top), kind="int",
+                          init=("distinct", 0, s.num_experts))]
+        for e in range(s.num_experts):
+            out += [TensorSpec(self._name("expert_gate", e), (s.intermediate_size, s.hidden_size)),
+                    TensorSpec(self._name("expert_up", e), (s.intermediate_size, s.hidden_size)),
+                    TensorSpec(self._name("expert_down", e), (s.hidden_size, s.intermediate_size))]
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        s = self.spec
+        self.table = tensors[self.names["expert_table"]].to(torch.int32).contiguous()
+        if self.table.numel() and (int(self.table.min()) < 0 or int(self.table.max()) >= s.num_experts):
+            raise ValueError(f"{self.names['expert_table']}: an entry names an expert outside 0..{s.num_experts - 1}")
+        first = tensors[self._name("expert_gate", 0)]
+        self.gate_up = torch.empty((s.num_experts, 2 * s.intermediate_size, s.hidden_size), dtype=first.dtype,
+                                   device=first.device)
+        self.down = torch.empty((s.num_experts, s.hidden_size, s.intermediate_size), dtype=first.dtype,
+                                device=first.device)
+        for e in range(s.num_experts):
+            self.gate_up[e, :s.intermediate_size] = tensors[self._name("expert_gate", e)]
+            self.gate_up[e, s.intermediate_size:] = tensors[self._name("expert_up", e)]
+            self.down[e] = tensors[self._name("expert_down", e)]
+
+    def launch_key(self, ctx):
+        return ()
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx) -> None:
+        s, k = self.spec, self.runtime.kernels
+        T = x.shape[0]
+        pairs = T * s.top
+        route = ctx.workspace.get("experts.route", (k.route_words(pairs, s.num_experts),), torch.int32)
+        act = ctx.workspace.get("experts.act", (pairs, s.intermediate_size), self.runtime.dtype)
+        y = ctx.workspace.get("experts.out", (pairs, s.hidden_size), torch.float32)
+        k.routed_experts(x, ctx.tokens, self.table, self.gate_up, self.down, residual, route, act, y,
+                         s.activation, 1.0 / s.top)
+        return None
+
+
 register_feed_forward("gated_mlp", GatedMLP, replace=True)
+register_feed_forward("table_experts", TableExperts, replace=True)
 register_feed_forward("mlp", DenseMLP, replace=True)

@@ -6,9 +6,16 @@ host, angle = float(position) * inv_freq[j] in 32-bit
 (src/metal/metal_kernels.mm:186-191, src/metal/kernels/tensor_ops.metal:168-197).
 The attention kernels apply it themselves from the table (``fused_rotation``).
 
+With ``scaling_factor`` the slow frequencies are stretched (see PositionSpec) and
+cosines and sines carry an amplitude other than one; the frequencies are then made
+in 64-bit on the host and rounded once.  Kernels that rotate from ``inv_freq`` alone
+do not know the amplitude: a mixer asks ``amplitude`` and takes a kernel that does.
+
 "none": no position information inside the mixer.
 """
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -23,13 +30,38 @@ def rotary_inverse_frequencies(theta: float, rotary_dim: int) -> torch.Tensor:
     return torch.pow(torch.tensor(float(theta), dtype=torch.float32), exponent)
 
 
+def stretched_inverse_frequencies(spec) -> torch.Tensor:
+    """The frequencies of a rotation whose slow part is divided by ``scaling_factor``:
+    pairs that turn more than ``fast_turns`` times within ``original_positions`` keep
+    their frequency, pairs that turn less than ``slow_turns`` times get all of the
+    factor, a linear ramp over the pair index lies between."""
+    n, theta = spec.rotary_dim, float(spec.theta)
+    j = torch.arange(n // 2, dtype=torch.float64)
+    freq = theta ** (-2.0 * j / n)
+
+    def pair_that_turns(times: float) -> float:
+        return n * math.log(spec.original_positions / (2.0 * math.pi * times)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(pair_that_turns(spec.fast_turns)), 0)
+    hi = min(math.ceil(pair_that_turns(spec.slow_turns)), n - 1)
+    ramp = ((j - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return (freq * (ramp / float(spec.scaling_factor) + (1.0 - ramp))).to(torch.float32)
+
+
 class RotaryEncoding(PositionEncoding):
     def __init__(self, spec, runtime: Runtime):
         if spec.rotary_dim % 2 != 0 or spec.rotary_dim > spec.head_dim or spec.rotary_dim <= 0:
             raise ValueError(f"rotary_dim {spec.rotary_dim} must be even and within head_dim {spec.head_dim}")
         self.spec = spec
         self.runtime = runtime
-        self.inv_freq = rotary_inverse_frequencies(spec.theta, spec.rotary_dim).to(runtime.device)
+        self.amplitude = 1.0
+        if spec.scaling_factor:
+            if spec.scaling_factor <= 0 or spec.original_positions <= 0 or spec.fast_turns <= 0 or spec.slow_turns <= 0:
+                raise ValueError("a stretched rotation needs positive factor, original positions and turn counts")
+            self.inv_freq = stretched_inverse_frequencies(spec).to(runtime.device)
+            self.amplitude = float(spec.amplitude_slope) * math.log(float(spec.scaling_factor)) + 1.0
+        else:
+            self.inv_freq = rotary_inverse_frequencies(spec.theta, spec.rotary_dim).to(runtime.device)
 
     def fused_rotation(self):
         return self.inv_freq, self.spec.rotary_dim
@@ -38,10 +70,15 @@ class RotaryEncoding(PositionEncoding):
         table_of = getattr(self.runtime.kernels, "rope_table", None)
         if table_of is None:
             return None
-        key = ("rope", float(self.spec.theta), int(self.spec.rotary_dim))
+        if self.amplitude != 1.0:
+            return None                      # the table's readers rotate with amplitude one
+        s = self.spec
+        key = ("rope", float(s.theta), int(s.rotary_dim), float(s.scaling_factor), int(s.original_positions),
+               float(s.fast_turns), float(s.slow_turns))
         table = ctx.shared.get(key)
         if table is None:
-            table = ctx.workspace.get(f"rope.table.{key[1]}.{key[2]}", (ctx.num_tokens, self.spec.rotary_dim),
+            table = ctx.workspace.get("rope.table." + ".".join(str(v) for v in key[1:]),
+                                      (ctx.num_tokens, self.spec.rotary_dim),
                                       torch.float32)
             table_of(ctx.positions, self.inv_freq, self.spec.rotary_dim, table)
             ctx.shared[key] = table
@@ -49,6 +86,8 @@ class RotaryEncoding(PositionEncoding):
 
 
 class NoPosition(PositionEncoding):
+    amplitude = 1.0
+
     def __init__(self, spec, runtime: Runtime):
         self.spec = spec
 

@@ -81,6 +81,16 @@ def _fill(out: torch.Tensor, key: int, normal: bool, init=None) -> None:
 def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype,
                   device: torch.device = torch.device("cpu")) -> torch.Tensor:
     if spec.kind == "int":
+        if spec.init is not None and spec.init[0] == "distinct":
+            # every row: shape[-1] different integers of low .. high - 1 (the first places of a random
+            # order of them; the order comes from the same counter-based generator)
+            low, high = int(spec.init[1]), int(spec.init[2])
+            rows = 1
+            for n in spec.shape[:-1]:
+                rows *= int(n)
+            keys = _mix(torch.arange(1, rows * (high - low) + 1, dtype=torch.int64, device=device), _key(seed, spec.name))
+            order = torch.argsort(keys.view(rows, high - low), dim=1, stable=True)[:, :spec.shape[-1]]
+            return (order + low).to(torch.int32).view(spec.shape).contiguous()
         return torch.zeros(spec.shape, dtype=torch.int32, device=device)
     t = torch.empty(spec.shape, dtype=dtype, device=device)
     if spec.init is not None and spec.init[0] not in ("normal", "uniform"):
