@@ -88,18 +88,21 @@ class ReferenceKernels:
 
     def attention(self, q, k_cache, v_cache, out, block_table, q_start, ctx_len, seq_of_token,
                   positions, nq, nkv, d, page_size, scale, window, max_q_len, max_ctx_len, min_q_len=0,
-                  seq_rows=None, softcap=None, distance_bias=None):
+                  seq_rows=None, softcap=None, distance_bias=None, chunk=None, value_dim=None):
         self._count("attention")
         T = q.shape[0]
         group = nq // nkv
+        dv = d if value_dim is None else value_dim
         qf = q.float().reshape(T, nq, d)
-        res = torch.zeros(T, nq, d, dtype=torch.float32, device=q.device)
+        res = torch.zeros(T, nq, dv, dtype=torch.float32, device=q.device)
         for t in range(T):
             s = int(seq_of_token[t])
             if seq_rows is not None:
                 s = int(seq_rows[s])
             p = int(positions[t])
             first = max(0, p - window + 1) if window else 0
+            if chunk:
+                first = max(first, p - p % chunk)
             idx = torch.arange(first, p + 1, device=q.device)
             pages = block_table[s, idx // page_size].long()
             assert (pages >= 0).all() and (pages < k_cache.shape[0]).all(), "attention outside the pool"
@@ -115,7 +118,87 @@ class ReferenceKernels:
                     sc = sc - r1[h].float() * torch.log1p(r2[h].float() * (p - idx).float())
                 pr = torch.softmax(sc, dim=0)
                 res[t, h] = pr @ vals[:, g, :]
-        out.copy_(res.reshape(T, nq * d).to(out.dtype))
+        out.copy_(res.reshape(T, nq * dv).to(out.dtype))
+
+    # ---- the operations of layer_ops.cu
+    def heads_rotate_append(self, qkv, q_out, k_cache, v_cache, inv_freq, rotary_dim, amplitude, unit_norm, eps,
+                            positions, seq_of_token, block_table, nq, nkv, d, dv, page_size, seq_rows=None):
+        self._count("heads_rotate_append")
+        T = qkv.shape[0]
+
+        def finish(x):
+            if rotary_dim:
+                half = rotary_dim // 2
+                angle = positions.float()[:, None] * inv_freq[:half].float()[None, :]
+                c, s = (torch.cos(angle) * amplitude)[:, None, :], (torch.sin(angle) * amplitude)[:, None, :]
+                lo, hi = x[..., :half], x[..., half:rotary_dim]
+                x = torch.cat([lo * c - hi * s, hi * c + lo * s, x[..., rotary_dim:]], dim=-1)
+            if unit_norm:
+                x = x * torch.rsqrt((x * x).sum(-1, keepdim=True) / d + eps)
+            return x
+
+        q_out.copy_(finish(qkv[:, :nq * d].float().reshape(T, nq, d)).reshape(T, nq * d).to(q_out.dtype))
+        if k_cache is None:
+            return
+        k = finish(qkv[:, nq * d:(nq + nkv) * d].float().reshape(T, nkv, d))
+        v = qkv[:, (nq + nkv) * d:(nq + nkv) * d + nkv * dv].float().reshape(T, nkv, dv)
+        pos = positions.long()
+        rows = seq_of_token.long() if seq_rows is None else seq_rows.long()[seq_of_token.long()]
+        pages = block_table[rows, pos // page_size].long()
+        assert (pages >= 0).all() and (pages < k_cache.shape[0]).all(), "append outside the pool"
+        k_cache[pages, :, pos % page_size, :] = k.to(k_cache.dtype)
+        v_cache[pages, :, pos % page_size, :] = v.to(v_cache.dtype)
+
+    def _act(self, z, kind):
+        t = z.clone()
+        self.activation(t, kind)
+        return t
+
+    def gated_activation(self, gate_up, bias, out, kind):
+        self._count("gated_activation")
+        n = out.shape[1]
+        gu = gate_up.float() + (bias.float() if bias is not None else 0.0)
+        out.copy_((self._act(gu[:, :n], kind) * gu[:, n:]).to(out.dtype))
+
+    def route_words(self, pairs, experts):
+        return 1
+
+    def routed_experts(self, x, tokens, table, gate_up, down, acc, route, act, y, kind, weight):
+        self._count("routed_experts")
+        F = down.shape[2]
+        for t in range(x.shape[0]):
+            total = torch.zeros_like(acc[t])
+            for e in table[int(tokens[t])].tolist():
+                gu = gate_up[e].float() @ x[t].float()
+                hidden = (self._act(gu[:F], kind) * gu[F:]).to(x.dtype).float()
+                total += down[e].float() @ hidden
+            acc[t] += weight * total
+
+    def layer_end(self, residual, delta, mult, side=None, y_in=None, norm=None):
+        self._count("layer_end")
+        if delta is not None:
+            residual.add_(mult * delta)
+        if side is not None:
+            tokens, table, offset, gate, proj, side_w, act, eps = side
+            if y_in is None:
+                e = table[tokens.long(), offset:offset + gate.shape[0]].float()
+                y = (self._act(residual @ gate.float().t(), act) * e) @ proj.float().t()
+            else:
+                y = y_in
+            residual.add_(mult * y * torch.rsqrt((y * y).mean(-1, keepdim=True) + eps) * side_w.float())
+        if norm is not None:
+            w, eps, offset, out = norm
+            self.rmsnorm(residual, w, eps, offset, out)
+
+    def side_gate(self, gate, tokens, table, offset, kind):
+        e = table[tokens.long(), offset:offset + gate.shape[1]].float()
+        gate.copy_((self._act(gate.float(), kind) * e).to(gate.dtype))
+
+    def softcap(self, x, cap):
+        x.copy_(cap * torch.tanh(x / cap))
+
+    def zero(self, x):
+        x.zero_()
 
     def apply_table_updates(self, table, updates, capacity):
         n = int(updates[0])
