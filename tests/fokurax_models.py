@@ -8,6 +8,11 @@ without any rotation, blocks of 5 to 128 positions and no blocks at all, layers
 that read the cache of a layer right before them or further back, layers
 without a feed-forward, dense ones, experts with one, two and three choices out
 of 3 to 12, with and without the token input, the logit cap and the scales.
+The token input has 11 features or more in these models: with 3 to 8 of them the direction
+of y = P g hangs on so few rounded numbers that, after y is divided by its root mean square,
+single positions of a bfloat16 run are 3 to 19 % of the largest logit away from the 32-bit
+result -- in the arithmetic of the stand-in kernels just as on the device -- while the median
+position stays at 0.3 %; the kernel's own test covers 3 and 5 features.
 The weights are made here, with torch's generator, and written with the
 ``safetensors`` library; nothing of the package takes part.
 """
@@ -30,7 +35,7 @@ def rot(dims, base=10000.0, factor=None, original=64, fast=32.0, slow=1.0):
 
 def layer(heads, kv_heads, dim, vdim=None, chunk=None, rotation=None, scale=None, kv_from=None, mlp=None):
     m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim if vdim is None else vdim,
-         "scale": scale if scale is not None else 1.0 / math.sqrt(dim) * 4.0}
+         "scale": scale if scale is not None else 2.0 / math.sqrt(dim)}
     if chunk is not None:
         m["mask"] = {"size": chunk}
     if rotation is not None:
@@ -52,7 +57,7 @@ CONFIGS: Dict[str, dict] = {
     # value heads smaller than key heads, two choices of five experts, blocks of 24 positions, a part of the
     # head rotated with stretched frequencies, the third layer reads the first one's cache
     "F1": {"architecture": "Fokurax", "vocab": 211, "width": 64, "norm": {"eps": 1e-6}, "embedding": {"scale": 3.0},
-           "residual_mult": 0.7, "logit_softcap": 9.0, "token_side": {"dim": 5},
+           "residual_mult": 0.7, "logit_softcap": 9.0, "token_side": {"dim": 13},
            "layers": [layer(4, 2, 32, vdim=16, chunk=24, rotation=rot(16, 5000.0, factor=4.0, original=32), mlp=dense(96)),
                       layer(4, 2, 32, vdim=16, chunk=24, rotation=rot(16, 5000.0, factor=4.0, original=32), mlp=moe(40, 5, 2)),
                       layer(4, 2, 32, vdim=16, chunk=24, rotation=rot(16, 5000.0, factor=4.0, original=32), kv_from=0,
@@ -76,13 +81,13 @@ CONFIGS: Dict[str, dict] = {
     # sizes that are no power of two anywhere: five query heads on one key head of 80, values of 40, blocks of 5
     # positions (shorter than a page), an odd vocabulary, seven experts
     "F4": {"architecture": "Fokurax", "vocab": 257, "width": 160, "norm": {"eps": 3e-6}, "embedding": {"scale": -1.5},
-           "residual_mult": 1.0, "logit_softcap": 30.0, "token_side": {"dim": 3},
+           "residual_mult": 1.0, "logit_softcap": 30.0, "token_side": {"dim": 11},
            "layers": [layer(5, 1, 80, vdim=40, chunk=5, rotation=rot(40, 300.0, factor=2.0, original=16, fast=4.0), mlp=moe(56, 7, 2)),
                       layer(2, 2, 24, vdim=24, chunk=37, rotation=rot(24, 777.0), mlp=dense(200)),
                       layer(5, 1, 80, vdim=40, chunk=5, rotation=rot(40, 300.0, factor=2.0, original=16, fast=4.0), kv_from=0)]},
     # one layer, one head, no rotation
     "F5": {"architecture": "Fokurax", "vocab": 97, "width": 48, "norm": {"eps": 1e-5}, "residual_mult": 1.25,
-           "token_side": {"dim": 8},
+           "token_side": {"dim": 16},
            "layers": [layer(1, 1, 40, vdim=8, chunk=64, mlp=moe(32, 3, 2))]},
 }
 

@@ -42,7 +42,7 @@ def test_parts_follow_the_file(tmp_path):
     assert [l.feed_forward.kind for l in spec.layers] == ["gated_mlp", "table_experts", "table_experts"]
     assert spec.layers[0].feed_forward.biases and spec.layers[0].feed_forward.activation == "gelu_tanh"
     assert (spec.layers[2].feed_forward.num_experts, spec.layers[2].feed_forward.top) == (3, 3)
-    assert [l.token_input.offset for l in spec.layers] == [0, 5, 10] and spec.shared_tensors[0][1] == (211, 15)
+    assert [l.token_input.offset for l in spec.layers] == [0, 13, 26] and spec.shared_tensors[0][1] == (211, 39)
     assert spec.final_norm.weight_offset == 1.0
     assert [a.kind for a in spec.input_adapters + spec.logit_adapters] == ["scale", "softcap"]
 
