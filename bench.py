@@ -15,8 +15,8 @@ its time, against the measured copy bandwidth; ``points`` decode at batch 1 and
 filled by real prefill steps for the end-to-end run and with random values for
 the device-timed runs (the work of a decode step does not depend on the values).
 
-``--design gitipel`` prints, instead of the record, prefill and decode of the
-Gitipel design beside Qwen3 at equal layer sizes, with the time of every kernel.
+``--design gitipel`` (or ``fokurax``) prints, instead of the record, prefill and decode of
+that design beside Qwen3 at equal layer sizes, with the time of every kernel.
 
 ``--timeline`` prints, instead of the record, when the CTAs of every kernel of one
 decode step started, waited and ended.  ``--shape`` runs the same at the Qwen3-0.6B or
@@ -377,7 +377,7 @@ def measure_products(cfg, rows, seconds=2.0):
 
 
 # ------------------------------------------------------------------ another design beside Qwen3
-# Layer sizes for ``--design gitipel``: (width, attention heads, kv heads, head size, feed-forward).
+# Layer sizes for ``--design``: (width, attention heads, kv heads, head size, feed-forward).
 DESIGN_SIZES = {"small": (1024, 16, 8, 64, 3072), "medium": (2048, 16, 8, 128, 6144),
                 "large": (4096, 32, 8, 128, 12288)}
 
@@ -392,6 +392,29 @@ def gitipel_config(width, heads, kv_heads, dim, ff, vocab=32768):
     return {"architecture": "Gitipel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
             "embedding": {"scale": 1.0}, "logit_scale": 1.0, "canon": {"taps": 4},
             "layers": [att, rec, att, rec], "loop": {"start": 0, "stop": 2, "times": 2}}
+
+
+def fokurax_config(width, heads, kv_heads, dim, ff, vocab=32768):
+    """Six layers: a dense one, then one with experts whose cache the next two read, twice
+    over (the second group has one reader).  Eight experts of half the dense size, two a
+    token, so every layer does the arithmetic of a dense one; attention in blocks of 1,024
+    positions, half of every head rotated with stretched frequencies; a token input of 256
+    features per layer."""
+    rot = {"base": 1e6, "dims": dim // 2, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+
+    def layer(mlp, kv_from=None):
+        m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+             "mask": {"size": 1024}, "rot": rot}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "attention", "mixer": m, "mlp": mlp}
+
+    dense = {"kind": "dense", "ff": ff}
+    experts = {"kind": "moe", "expert": {"ff": ff // 2}, "router": {"experts": 8, "top": 2}}
+    return {"architecture": "Fokurax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0}, "residual_mult": 0.5, "logit_softcap": 30.0, "token_side": {"dim": 256},
+            "layers": [layer(dense), layer(experts), layer(experts, 1), layer(experts, 1), layer(dense),
+                       layer(experts, 4)]}
 
 
 def qwen3_config_like(width, heads, kv_heads, dim, ff, layers=6, vocab=32768):
@@ -460,16 +483,17 @@ def measure_design(name, cfg, vocab, prompt_tokens, batch, held, steps, warmup, 
     return out
 
 
-def compare_designs(sizes, prompt_tokens, batch, held, steps, warmup):
-    """Gitipel beside Qwen3 at equal layer sizes (six layer runs each, random weights)."""
-    result = {"metric": "prefill and decode of Gitipel beside Qwen3 at equal layer sizes", "layer_runs": 6,
+def compare_designs(sizes, prompt_tokens, batch, held, steps, warmup, design="gitipel"):
+    """Another design beside Qwen3 at equal layer sizes (six layer runs each, random weights)."""
+    make = {"gitipel": gitipel_config, "fokurax": fokurax_config}[design]
+    result = {"metric": f"prefill and decode of {design.capitalize()} beside Qwen3 at equal layer sizes", "layer_runs": 6,
               "prompt_tokens": prompt_tokens, "decode_batch": batch, "decode_tokens_held": held, "dtype": "bf16",
               "data": "synthetic", "sizes": {}}
     for size in sizes:
         width, heads, kv_heads, dim, ff = DESIGN_SIZES[size]
         entry = {"width": width, "heads": heads, "kv_heads": kv_heads, "head_dim": dim, "ff": ff}
-        entry["gitipel"] = measure_design("g", gitipel_config(width, heads, kv_heads, dim, ff), 32768, prompt_tokens,
-                                          batch, held, steps, warmup)
+        entry[design] = measure_design(design[0], make(width, heads, kv_heads, dim, ff), 32768, prompt_tokens,
+                                       batch, held, steps, warmup)
         entry["qwen3"] = measure_design("q", qwen3_config_like(width, heads, kv_heads, dim, ff), 32768, prompt_tokens,
                                         batch, held, steps, warmup)
         result["sizes"][size] = entry
@@ -553,7 +577,7 @@ def main() -> int:
     ap.add_argument("--check-tokens", type=int, default=0,
                     help="with --mixed-requests: also generate this many tokens of every request with the 32-bit "
                          "engine under two budgets and report how the runs agree")
-    ap.add_argument("--design", default=None, choices=["gitipel"],
+    ap.add_argument("--design", default=None, choices=["gitipel", "fokurax"],
                     help="instead of the record: prefill and decode of this design beside Qwen3 at equal layer "
                          "sizes (--design-sizes), with the time of every kernel")
     ap.add_argument("--design-sizes", default="small,medium,large",
@@ -591,7 +615,7 @@ def main() -> int:
             print(f"unknown --design-sizes {unknown}; known: {sorted(DESIGN_SIZES)}")
             return 2
         print(json.dumps(compare_designs(sizes, args.prefill_tokens, args.batch, args.prompt, min(args.steps, 64),
-                                         args.warmup)), flush=True)
+                                         args.warmup, args.design)), flush=True)
         return 0
     if args.products:
         print(json.dumps(measure_products(cfg, args.prefill_tokens)), flush=True)

@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(256)
 expert_rows_gemm_kernel(const TA* __restrict__ a, long long a_stride, const int* __restrict__ a_index, int a_div,
                         const TW* __restrict__ w, long long w_expert_stride, TO* __restrict__ out,
                         long long out_stride, const int* __restrict__ offsets, const int* __restrict__ tile_expert,
-                        const int* __restrict__ tile_row0, int N, int K, int kind)
+                        const int* __restrict__ tile_row0, int N, int K, int kind, int interleaved)
 {
     pdl_enter();
     const int expert = tile_expert[blockIdx.y];
@@ -225,6 +225,10 @@ expert_rows_gemm_kernel(const TA* __restrict__ a, long long a_stride, const int*
     if (ar < row_end)
         a_row = a_index ? a_index[ar] / a_div : ar;
     const int bn = n0 + lr;
+    // rows of the gate and of the up matrix for column bn: gate rows then up rows, or (interleaved) blocks
+    // of 16 gate rows followed by their 16 up rows
+    const size_t gate_row = (GATED && interleaved) ? (size_t)(bn / 16) * 32 + bn % 16 : (size_t)bn;
+    const size_t up_row = (GATED && interleaved) ? gate_row + 16 : (size_t)N + bn;
     float acc[GATED ? 2 : 1][4][4];
 #pragma unroll
     for (int g = 0; g < (GATED ? 2 : 1); ++g)
@@ -238,9 +242,9 @@ expert_rows_gemm_kernel(const TA* __restrict__ a, long long a_stride, const int*
         for (int u = 0; u < 4; ++u) {
             const int k = k0 + lk + u;
             As[lk + u][lr] = (a_row >= 0 && k < K) ? to_f32(a[a_row * a_stride + k]) : 0.f;
-            Bs[0][lk + u][lr] = (bn < N && k < K) ? to_f32(we[(size_t)bn * K + k]) : 0.f;
+            Bs[0][lk + u][lr] = (bn < N && k < K) ? to_f32(we[gate_row * K + k]) : 0.f;
             if (GATED)
-                Bs[GATED ? 1 : 0][lk + u][lr] = (bn < N && k < K) ? to_f32(we[(size_t)(N + bn) * K + k]) : 0.f;
+                Bs[GATED ? 1 : 0][lk + u][lr] = (bn < N && k < K) ? to_f32(we[up_row * K + k]) : 0.f;
         }
         __syncthreads();
 #pragma unroll
@@ -278,6 +282,158 @@ expert_rows_gemm_kernel(const TA* __restrict__ a, long long a_stride, const int*
             if (GATED)
                 v = activate(v, kind) * acc[GATED ? 1 : 0][i][j];
             out[(size_t)r * out_stride + n] = from_f32<TO>(v);
+        }
+    }
+}
+
+// The same product on the tensor cores (bfloat16, 32-bit sums): tiles of 128 rows of one expert
+// times 128 columns, K in blocks of 32 through three stages of cp.async, eight warps of 64 x 32
+// sums each (mma.sync m16n8k16).  Rows that a tile does not have are filled with zeros and not
+// stored, so a decode step's tiles of one or two rows stream their expert's weights once.
+// GATED: the expert's matrix holds blocks of 16 gate rows followed by their 16 up rows, so a
+// warp's 32 columns are 16 gate sums and the 16 up sums that belong to them, in the same lanes.
+constexpr int TG_M = 128, TG_N = 128, TG_K = 32, TG_PAD = 40, TG_STAGES = 3;
+
+__device__ __forceinline__ void tg_cp_async16(void* dst, const void* src, bool valid)
+{
+    const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tg_ldmatrix_x4(uint32_t (&r)[4], const void* p)
+{
+    const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(a));
+}
+__device__ __forceinline__ void tg_mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+                 "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(256)
+expert_rows_mma_kernel(const __nv_bfloat16* __restrict__ a, long long a_stride, const int* __restrict__ a_index,
+                       int a_div, const __nv_bfloat16* __restrict__ w, long long w_expert_stride, void* __restrict__ out,
+                       long long out_stride, const int* __restrict__ offsets, const int* __restrict__ tile_expert,
+                       const int* __restrict__ tile_row0, int N, int K, int kind)
+{
+    pdl_enter();
+    const int expert = tile_expert[blockIdx.y];
+    if (expert < 0)
+        return;
+    const int row0 = tile_row0[blockIdx.y];
+    const int row_end = min(row0 + TG_M, offsets[expert + 1]);
+    const int n0 = blockIdx.x * TG_N;
+    extern __shared__ __align__(16) unsigned char tg_raw[];
+    __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(tg_raw);             // [stage][TG_M][TG_PAD]
+    __nv_bfloat16* Bs = As + TG_STAGES * TG_M * TG_PAD;                       // [stage][TG_N][TG_PAD]
+    const __nv_bfloat16* we = w + (size_t)expert * w_expert_stride;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int warp_m = warp >> 2, warp_n = warp & 3;
+
+    // what this thread brings in per K block: two 16-byte pieces of the rows' tile, two of the weights'
+    const __nv_bfloat16* a_src[2];
+    const __nv_bfloat16* b_src[2];
+    bool a_ok[2], b_ok[2];
+    int dst_off[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int c = tid + i * 256;
+        const int r = c >> 2, part = c & 3;
+        dst_off[i] = r * TG_PAD + part * 8;
+        const int ar = row0 + r;
+        a_ok[i] = ar < row_end;
+        const long long src_row = a_ok[i] ? (a_index ? a_index[ar] / a_div : ar) : 0;
+        a_src[i] = a + src_row * a_stride + part * 8;
+        b_ok[i] = n0 + r < N;
+        b_src[i] = we + (size_t)(b_ok[i] ? n0 + r : 0) * K + part * 8;
+    }
+    auto issue = [&](int kt, int stage) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            tg_cp_async16(As + (size_t)stage * TG_M * TG_PAD + dst_off[i], a_src[i] + (size_t)kt * TG_K, a_ok[i]);
+            tg_cp_async16(Bs + (size_t)stage * TG_N * TG_PAD + dst_off[i], b_src[i] + (size_t)kt * TG_K, b_ok[i]);
+        }
+    };
+    float acc[4][4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                acc[i][j][e] = 0.f;
+    const int KT = K / TG_K;
+#pragma unroll
+    for (int s = 0; s < TG_STAGES - 1; ++s) {
+        if (s < KT)
+            issue(s, s);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int kt = 0; kt < KT; ++kt) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(TG_STAGES - 2) : "memory");
+        __syncthreads();                       // block kt has landed for everybody, and block kt - 1 has been used by everybody
+        const int next = kt + TG_STAGES - 1;
+        if (next < KT)
+            issue(next, next % TG_STAGES);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const __nv_bfloat16* At = As + (size_t)(kt % TG_STAGES) * TG_M * TG_PAD;
+        const __nv_bfloat16* Bt = Bs + (size_t)(kt % TG_STAGES) * TG_N * TG_PAD;
+#pragma unroll
+        for (int ks = 0; ks < TG_K / 16; ++ks) {
+            uint32_t af[4][4], bf[2][4];
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi)
+                tg_ldmatrix_x4(af[mi], At + (warp_m * 64 + mi * 16 + (lane & 15)) * TG_PAD + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int np = 0; np < 2; ++np)
+                tg_ldmatrix_x4(bf[np], Bt + (warp_n * 32 + np * 16 + (lane >> 4) * 8 + (lane & 7)) * TG_PAD + ks * 16
+                                           + ((lane >> 3) & 1) * 8);
+#pragma unroll
+            for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+                for (int np = 0; np < 2; ++np) {
+                    tg_mma_bf16(acc[mi][2 * np], af[mi], bf[np][0], bf[np][1]);
+                    tg_mma_bf16(acc[mi][2 * np + 1], af[mi], bf[np][2], bf[np][3]);
+                }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int mi = 0; mi < 4; ++mi) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = row0 + warp_m * 64 + mi * 16 + (lane >> 2) + half * 8;
+            if (r >= row_end)
+                continue;
+            if (GATED) {
+                __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(out) + (size_t)r * out_stride;
+                const int base = (n0 + warp_n * 32) / 2;
+#pragma unroll
+                for (int ni = 0; ni < 2; ++ni)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int col = base + ni * 8 + (lane & 3) * 2 + e;
+                        if (col < N / 2)
+                            orow[col] = __float2bfloat16_rn(activate(acc[mi][ni][half * 2 + e], kind)
+                                                            * acc[mi][ni + 2][half * 2 + e]);
+                    }
+            } else {
+                float* orow = static_cast<float*>(out) + (size_t)r * out_stride;
+#pragma unroll
+                for (int ni = 0; ni < 4; ++ni)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int col = n0 + warp_n * 32 + ni * 8 + (lane & 3) * 2 + e;
+                        if (col < N)
+                            orow[col] = acc[mi][ni][half * 2 + e];
+                    }
+            }
         }
     }
 }
@@ -486,57 +642,86 @@ CHIBI_API int chibi_gated_activation(const void* gate_up, int x_type, long long 
 // route: int32 scratch of (experts + 1) + 2 pairs + 2 max_tiles values (max_tiles = ceil(pairs / chibi_expert_tile_rows()) + experts), laid out as
 // offsets[experts + 1] | pair_of_row[pairs] | row_of_pair[pairs] | tile_expert[max_tiles] | tile_row0[max_tiles]
 CHIBI_API int chibi_expert_tile_rows() { return EG_M; }
+CHIBI_API int chibi_expert_tile_rows_tensor_cores() { return TG_M; }
 
 CHIBI_API int chibi_route_by_table(const int* tokens, const int* table, int vocab, int top, int experts,
-                                   long long num_tokens, int* route, int* error, cudaStream_t stream)
+                                   long long num_tokens, int tile_rows, int* route, int* error, cudaStream_t stream)
 {
     if (num_tokens <= 0)
         return CHIBI_OK;
-    if (!tokens || !table || !route || top <= 0 || experts <= 0 || vocab <= 0)
+    if (!tokens || !table || !route || top <= 0 || experts <= 0 || vocab <= 0 || (tile_rows != EG_M && tile_rows != TG_M))
         return CHIBI_ERR_ARGUMENT;
     const long long pairs = num_tokens * top;
     if (pairs > (1LL << 24) || experts > 4096)
         return CHIBI_ERR_UNSUPPORTED;
-    const int max_tiles = (int)((pairs + EG_M - 1) / EG_M) + experts;
+    const int max_tiles = (int)((pairs + tile_rows - 1) / tile_rows) + experts;
     int* offsets = route;
     int* pair_of_row = offsets + experts + 1;
     int* row_of_pair = pair_of_row + pairs;
     int* tile_expert = row_of_pair + pairs;
     int* tile_row0 = tile_expert + max_tiles;
     launch(route_by_table_kernel, dim3(1), dim3(1024), (size_t)2 * experts * sizeof(int), stream, tokens, table, vocab,
-           top, experts, (int)num_tokens, EG_M, max_tiles, offsets, pair_of_row, row_of_pair, tile_expert, tile_row0,
+           top, experts, (int)num_tokens, tile_rows, max_tiles, offsets, pair_of_row, row_of_pair, tile_expert, tile_row0,
            error);
     return launch_status();
 }
 
 // One product of the routed rows.  gated != 0: w [experts, 2 N, K], out = act(gate) * up in a's type;
 // else w [experts, N, K], out 32-bit.  gather != 0: row r of the product reads a[pair_of_row[r] / top].
+// tile_rows is what the route was made with: 64 runs the plain kernel (any types and sizes; with
+// interleaved != 0 a gated matrix holds blocks of 16 gate rows and their 16 up rows), 128 the
+// tensor-core kernel (bfloat16, K a multiple of 32, gated matrices interleaved, N a multiple of 16).
 CHIBI_API int chibi_expert_rows_gemm(const void* a, int a_type, long long a_stride, int gather, int top, const void* w,
                                      int w_type, void* out, long long out_stride, const int* route, long long pairs,
-                                     int experts, int N, int K, int gated, int kind, cudaStream_t stream)
+                                     int experts, int N, int K, int gated, int kind, int tile_rows, int interleaved,
+                                     cudaStream_t stream)
 {
     if (pairs <= 0)
         return CHIBI_OK;
-    if (!a || !w || !out || !route || N <= 0 || K <= 0 || experts <= 0 || top <= 0)
+    if (!a || !w || !out || !route || N <= 0 || K <= 0 || experts <= 0 || top <= 0
+        || (tile_rows != EG_M && tile_rows != TG_M))
         return CHIBI_ERR_ARGUMENT;
-    const int max_tiles = (int)((pairs + EG_M - 1) / EG_M) + experts;
+    const int max_tiles = (int)((pairs + tile_rows - 1) / tile_rows) + experts;
     if (max_tiles > 65535)
         return CHIBI_ERR_UNSUPPORTED;
     const int* offsets = route;
     const int* pair_of_row = offsets + experts + 1;
     const int* tile_expert = pair_of_row + 2 * pairs;
     const int* tile_row0 = tile_expert + max_tiles;
-    const dim3 grid((unsigned)((N + EG_N - 1) / EG_N), (unsigned)max_tiles);
     const long long w_stride = (long long)(gated ? 2 : 1) * N * K;
+    if (tile_rows == TG_M) {
+        if (a_type != CHIBI_BF16 || w_type != CHIBI_BF16 || K % TG_K != 0 || a_stride % 8 != 0
+            || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)
+            || (gated && (!interleaved || N % 16 != 0)))
+            return CHIBI_ERR_UNSUPPORTED;
+        const int rows_of_w = gated ? 2 * N : N;
+        const dim3 tgrid((unsigned)((rows_of_w + TG_N - 1) / TG_N), (unsigned)max_tiles);
+        const size_t smem = (size_t)TG_STAGES * (TG_M + TG_N) * TG_PAD * sizeof(__nv_bfloat16);
+        if (gated) {
+            auto kernel = expert_rows_mma_kernel<true>;
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            launch(kernel, tgrid, dim3(256), smem, stream, (const __nv_bfloat16*)a, a_stride,
+                   gather ? pair_of_row : (const int*)nullptr, top, (const __nv_bfloat16*)w, w_stride, out, out_stride,
+                   offsets, tile_expert, tile_row0, rows_of_w, K, kind);
+        } else {
+            auto kernel = expert_rows_mma_kernel<false>;
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            launch(kernel, tgrid, dim3(256), smem, stream, (const __nv_bfloat16*)a, a_stride,
+                   gather ? pair_of_row : (const int*)nullptr, top, (const __nv_bfloat16*)w, w_stride, out, out_stride,
+                   offsets, tile_expert, tile_row0, rows_of_w, K, kind);
+        }
+        return launch_status();
+    }
+    const dim3 grid((unsigned)((N + EG_N - 1) / EG_N), (unsigned)max_tiles);
     CHIBI_DISPATCH_TYPE(a_type, TA, CHIBI_DISPATCH_TYPE(w_type, TW, {
         if (gated)
             launch(expert_rows_gemm_kernel<TA, TW, TA, true>, grid, dim3(256), 0, stream, (const TA*)a, a_stride,
                    gather ? pair_of_row : (const int*)nullptr, top, (const TW*)w, w_stride, (TA*)out, out_stride,
-                   offsets, tile_expert, tile_row0, N, K, kind);
+                   offsets, tile_expert, tile_row0, N, K, kind, interleaved);
         else
             launch(expert_rows_gemm_kernel<TA, TW, float, false>, grid, dim3(256), 0, stream, (const TA*)a, a_stride,
                    gather ? pair_of_row : (const int*)nullptr, top, (const TW*)w, w_stride, (float*)out, out_stride,
-                   offsets, tile_expert, tile_row0, N, K, kind);
+                   offsets, tile_expert, tile_row0, N, K, kind, 0);
     }));
     return launch_status();
 }

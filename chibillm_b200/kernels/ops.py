@@ -1192,14 +1192,28 @@ class CudaKernels:
         tile = int(self.lib.chibi_expert_tile_rows())
         return (experts + 1) + 2 * pairs + 2 * ((pairs + tile - 1) // tile + experts)
 
+    def expert_tensor_cores(self, dtype: torch.dtype, hidden: int, inner: int) -> bool:
+        """Whether ``routed_experts`` runs experts of these sizes on the tensor cores; their
+        gate | up matrices are then to be stacked with ``interleave_expert_gate_up``."""
+        return self.use_tensor_cores and dtype == torch.bfloat16 and hidden % 32 == 0 and inner % 32 == 0
+
+    @staticmethod
+    def interleave_expert_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+        """[2 F, D]: blocks of 16 gate rows, each followed by its 16 up rows (F a multiple of 16)."""
+        F, D = gate.shape
+        return torch.stack([gate.view(F // 16, 16, D), up.view(F // 16, 16, D)], dim=1).reshape(2 * F, D)
+
     def routed_experts(self, x: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, gate_up: torch.Tensor,
                        down: torch.Tensor, acc: torch.Tensor, route: torch.Tensor, act: torch.Tensor,
-                       y: torch.Tensor, kind: str, weight: float) -> None:
+                       y: torch.Tensor, kind: str, weight: float, interleaved: bool = False) -> None:
         """acc[t] += weight * sum over the experts that ``table[tokens[t]]`` names (in the
         table's order) of down_e (act(gate_e x[t]) * (up_e x[t])).  gate_up [E, 2 F, D]
         (gate rows first), down [E, D, F], table int32 [vocab, top]; scratch: route int32
         (``route_words``), act [T top, F] in x's type, y float32 [T top, D].  Four
-        launches; nothing is read on the host."""
+        launches; nothing is read on the host.  ``interleaved``: gate_up's experts hold
+        blocks of 16 gate rows and their 16 up rows (``interleave_expert_gate_up``); with
+        bfloat16 and sizes that are multiples of 32 the products then run on the tensor
+        cores."""
         _need_cuda(x, tokens, table, gate_up, down, acc, route, act, y)
         _rows_contiguous(x, "routed_experts: x")
         _rows_contiguous(acc, "routed_experts: acc")
@@ -1218,13 +1232,20 @@ class CudaKernels:
             raise KernelError("routed_experts: shapes or types")
         stream = self._stream()
         self.launches += 4
-        _check(self.lib.chibi_route_by_table(_ptr(tokens), _ptr(table), vocab, top, E, T, _ptr(route),
+        fast = interleaved and gate_up.dtype == torch.bfloat16 and self.expert_tensor_cores(x.dtype, D, F) \
+            and x.stride(0) % 8 == 0
+        tile = int(self.lib.chibi_expert_tile_rows_tensor_cores() if fast else self.lib.chibi_expert_tile_rows())
+        flag = 1 if interleaved else 0
+        _check(self.lib.chibi_route_by_table(_ptr(tokens), _ptr(table), vocab, top, E, T, tile, _ptr(route),
                                              _ptr(self.error), stream), "routed_experts (route)")
         _check(self.lib.chibi_expert_rows_gemm(_ptr(x), _code(x), x.stride(0), 1, top, _ptr(gate_up), _code(gate_up),
                                                _ptr(act), F, _ptr(route), pairs, E, F, D, 1, self.ACTIVATIONS[kind],
-                                               stream), "routed_experts (gate | up)")
+                                               tile, flag, stream), "routed_experts (gate | up)")
         _check(self.lib.chibi_expert_rows_gemm(_ptr(act), _code(act), F, 0, top, _ptr(down), _code(down), _ptr(y), D,
-                                               _ptr(route), pairs, E, D, F, 0, 0, stream), "routed_experts (down)")
+                                               _ptr(route), pairs, E, D, F, 0, 0, tile, 0, stream),
+               "routed_experts (down)")
+        if fast:
+            self.tensor_core_calls += 2
         _check(self.lib.chibi_combine_experts(_ptr(y), _ptr(route), _ptr(acc), acc.stride(0), T, D, top, E,
                                               float(weight), stream), "routed_experts (combine)")
 

@@ -142,7 +142,10 @@ class TableExperts(FeedForward):
         self.names = names
         self.runtime = runtime
         self.table: torch.Tensor = None
-        self.gate_up: torch.Tensor = None       # [experts, 2 ff, hidden]: an expert's gate rows, then its up rows
+        # [experts, 2 ff, hidden]: an expert's gate rows, then its up rows -- or, for kernels that
+        # want it so, blocks of 16 gate rows each followed by its 16 up rows (``interleaved``)
+        self.gate_up: torch.Tensor = None
+        self.interleaved = False
         self.down: torch.Tensor = None          # [experts, hidden, ff]
 
     def _name(self, role: str, e: int) -> str:
@@ -168,9 +171,15 @@ class TableExperts(FeedForward):
                                    device=first.device)
         self.down = torch.empty((s.num_experts, s.hidden_size, s.intermediate_size), dtype=first.dtype,
                                 device=first.device)
+        fast = getattr(self.runtime.kernels, "expert_tensor_cores", None)
+        self.interleaved = fast is not None and fast(first.dtype, s.hidden_size, s.intermediate_size)
         for e in range(s.num_experts):
-            self.gate_up[e, :s.intermediate_size] = tensors[self._name("expert_gate", e)]
-            self.gate_up[e, s.intermediate_size:] = tensors[self._name("expert_up", e)]
+            gate, up = tensors[self._name("expert_gate", e)], tensors[self._name("expert_up", e)]
+            if self.interleaved:
+                self.gate_up[e] = self.runtime.kernels.interleave_expert_gate_up(gate, up)
+            else:
+                self.gate_up[e, :s.intermediate_size] = gate
+                self.gate_up[e, s.intermediate_size:] = up
             self.down[e] = tensors[self._name("expert_down", e)]
 
     def launch_key(self, ctx):
@@ -184,7 +193,7 @@ class TableExperts(FeedForward):
         act = ctx.workspace.get("experts.act", (pairs, s.intermediate_size), self.runtime.dtype)
         y = ctx.workspace.get("experts.out", (pairs, s.hidden_size), torch.float32)
         k.routed_experts(x, ctx.tokens, self.table, self.gate_up, self.down, residual, route, act, y,
-                         s.activation, 1.0 / s.top)
+                         s.activation, 1.0 / s.top, **({"interleaved": True} if self.interleaved else {}))
         return None
 
 

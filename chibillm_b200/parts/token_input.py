@@ -17,8 +17,10 @@ import torch
 
 from .base import Part, Runtime, TensorSpec
 
-# up to so many tokens the kernel at a layer's end does the two small products itself
+# up to so many tokens the kernel at a layer's end does the two small products itself, if the two
+# matrices are small too (a block per token reads both of them)
 FEW_TOKENS = 64
+SMALL_MATRIX = 16384
 
 
 class TokenInput(Part):
@@ -56,7 +58,8 @@ class TokenInput(Part):
     def wants_products(self, tokens: int) -> bool:
         """Whether the two products run as matrix products of their own (many tokens)
         or inside the kernel at the layer's end."""
-        return tokens > FEW_TOKENS and getattr(self.runtime.kernels, "side_gate", None) is not None
+        large = tokens > FEW_TOKENS or self.spec.dim * self.spec.hidden_size > SMALL_MATRIX
+        return large and getattr(self.runtime.kernels, "side_gate", None) is not None
 
     def products(self, residual: torch.Tensor, ctx) -> torch.Tensor:
         """y [T, hidden] float32 = P (act(G x) * e) by matrix products."""

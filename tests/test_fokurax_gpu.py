@@ -184,10 +184,12 @@ def test_gated_activation_with_biases(kernels, dtype, kind):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("T,D,F,E,top", [(1, 64, 40, 5, 2), (9, 96, 24, 3, 3), (300, 80, 100, 7, 1), (700, 128, 64, 4, 2),
-                                         (33, 72, 130, 12, 5)])
+                                         (33, 72, 130, 12, 5), (3, 96, 32, 6, 2), (1000, 160, 96, 5, 3),
+                                         (130, 256, 224, 3, 1)])
 def test_experts_chosen_by_a_table(kernels, dtype, T, D, F, E, top):
     """Few tokens (every tile holds a row or two), many (several tiles an expert), sizes
-    that end inside a tile, tokens that repeat, experts that nobody uses."""
+    that end inside a tile, tokens that repeat, experts that nobody uses.  With sizes that
+    are multiples of 32 the bfloat16 runs take the tensor-core kernel, else the plain one."""
     g = torch.Generator().manual_seed(T + E)
     dt = DTYPES[dtype]
     V = 50
@@ -203,14 +205,20 @@ def test_experts_chosen_by_a_table(kernels, dtype, T, D, F, E, top):
         w[f"m.e{e}.down"] = (torch.randn(D, F, generator=g) / math.sqrt(F)).to(dt)
     ref = plain.routed_feed_forward(x.double(), tokens, {"router": {"top": top}},
                                     {n: (t.double() if t.is_floating_point() else t) for n, t in w.items()}, "m.")
-    gate_up = torch.stack([torch.cat([w[f"m.e{e}.gate"], w[f"m.e{e}.up"]]) for e in range(E)]).to(DEV)
+    fast = kernels.expert_tensor_cores(dt, D, F)
+    if fast:        # blocks of 16 gate rows and their 16 up rows, as the tensor-core kernel wants them
+        gate_up = torch.stack([kernels.interleave_expert_gate_up(w[f"m.e{e}.gate"], w[f"m.e{e}.up"])
+                               for e in range(E)]).to(DEV)
+    else:
+        gate_up = torch.stack([torch.cat([w[f"m.e{e}.gate"], w[f"m.e{e}.up"]]) for e in range(E)]).to(DEV)
     down = torch.stack([w[f"m.e{e}.down"] for e in range(E)]).to(DEV)
     start = torch.randn(T, D, generator=g)
     acc = start.clone().to(DEV)
     route = torch.empty(kernels.route_words(T * top, E), dtype=torch.int32, device=DEV)
     act = torch.empty(T * top, F, dtype=dt, device=DEV)
     y = torch.empty(T * top, D, dtype=torch.float32, device=DEV)
-    kernels.routed_experts(x.to(DEV), tokens.to(DEV), table.to(DEV), gate_up, down, acc, route, act, y, "silu", 1.0 / top)
+    kernels.routed_experts(x.to(DEV), tokens.to(DEV), table.to(DEV), gate_up, down, acc, route, act, y, "silu", 1.0 / top,
+                           interleaved=fast)
     kernels.check_error_word()
     close(acc.cpu() - start, ref, 2e-5 if dtype == "float32" else 2e-2, "experts")
 
