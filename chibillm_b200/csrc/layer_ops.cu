@@ -369,6 +369,9 @@ expert_rows_mma_kernel(const __nv_bfloat16* __restrict__ a, long long a_stride, 
             for (int e = 0; e < 4; ++e)
                 acc[i][j][e] = 0.f;
     const int KT = K / TG_K;
+    // blocks of 16 rows of this warp's 64 that hold a row at all: a decode step's tile of a few rows
+    // costs its one block, not eight
+    const int m_tiles = max(0, min(4, (row_end - row0 - warp_m * 64 + 15) / 16));
 #pragma unroll
     for (int s = 0; s < TG_STAGES - 1; ++s) {
         if (s < KT)
@@ -384,23 +387,29 @@ expert_rows_mma_kernel(const __nv_bfloat16* __restrict__ a, long long a_stride, 
         asm volatile("cp.async.commit_group;" ::: "memory");
         const __nv_bfloat16* At = As + (size_t)(kt % TG_STAGES) * TG_M * TG_PAD;
         const __nv_bfloat16* Bt = Bs + (size_t)(kt % TG_STAGES) * TG_N * TG_PAD;
+        if (m_tiles == 0)
+            continue;
 #pragma unroll
         for (int ks = 0; ks < TG_K / 16; ++ks) {
             uint32_t af[4][4], bf[2][4];
 #pragma unroll
             for (int mi = 0; mi < 4; ++mi)
-                tg_ldmatrix_x4(af[mi], At + (warp_m * 64 + mi * 16 + (lane & 15)) * TG_PAD + ks * 16 + (lane >> 4) * 8);
+                if (mi < m_tiles)
+                    tg_ldmatrix_x4(af[mi], At + (warp_m * 64 + mi * 16 + (lane & 15)) * TG_PAD + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
             for (int np = 0; np < 2; ++np)
                 tg_ldmatrix_x4(bf[np], Bt + (warp_n * 32 + np * 16 + (lane >> 4) * 8 + (lane & 7)) * TG_PAD + ks * 16
                                            + ((lane >> 3) & 1) * 8);
 #pragma unroll
-            for (int mi = 0; mi < 4; ++mi)
+            for (int mi = 0; mi < 4; ++mi) {
+                if (mi >= m_tiles)
+                    continue;
 #pragma unroll
                 for (int np = 0; np < 2; ++np) {
                     tg_mma_bf16(acc[mi][2 * np], af[mi], bf[np][0], bf[np][1]);
                     tg_mma_bf16(acc[mi][2 * np + 1], af[mi], bf[np][2], bf[np][3]);
                 }
+            }
         }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -464,8 +473,8 @@ layer_end_kernel(float* __restrict__ residual, const float* __restrict__ delta, 
                  const int* __restrict__ tokens, const TW* __restrict__ side_table, long long table_stride,
                  int table_offset, int vocab, const TW* __restrict__ side_gate, const TW* __restrict__ side_proj,
                  const TW* __restrict__ side_norm, const float* __restrict__ y_in, int side, int kind, float eps,
-                 const TW* __restrict__ norm_w, float norm_offset, TO* __restrict__ norm_out, int n,
-                 int* __restrict__ error)
+                 const TW* __restrict__ norm_w, float norm_offset, TO* __restrict__ norm_out,
+                 TO* __restrict__ copy_out, int n, int* __restrict__ error)
 {
     pdl_enter();
     extern __shared__ float sm[];
@@ -529,6 +538,8 @@ layer_end_kernel(float* __restrict__ residual, const float* __restrict__ delta, 
     for (int c = tid; c < n; c += blockDim.x) {
         const float v = xs[c];
         xr[c] = v;
+        if (copy_out)
+            copy_out[t * n + c] = from_f32<TO>(v);      // the new residual in the activations' type
         ssq = fmaf(v, v, ssq);
     }
     if (!norm_out)
@@ -743,7 +754,8 @@ CHIBI_API int chibi_layer_end(float* residual, const float* delta, float mult, c
                               const void* side_table, long long table_stride, int table_offset, int vocab,
                               const void* side_gate, const void* side_proj, const void* side_norm, const float* y_in,
                               int side, int kind, float eps, const void* norm_w, float norm_offset, void* norm_out,
-                              int out_type, int w_type, long long rows, int n, int* error, cudaStream_t stream)
+                              void* copy_out, int out_type, int w_type, long long rows, int n, int* error,
+                              cudaStream_t stream)
 {
     if (rows <= 0)
         return CHIBI_OK;
@@ -762,7 +774,8 @@ CHIBI_API int chibi_layer_end(float* residual, const float* delta, float mult, c
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         launch(kernel, dim3((unsigned)rows), dim3(256), smem, stream, residual, delta, mult, tokens,
                (const TW*)side_table, table_stride, table_offset, vocab, (const TW*)side_gate, (const TW*)side_proj,
-               (const TW*)side_norm, y_in, side, kind, eps, (const TW*)norm_w, norm_offset, (TO*)norm_out, n, error);
+               (const TW*)side_norm, y_in, side, kind, eps, (const TW*)norm_w, norm_offset, (TO*)norm_out,
+               (TO*)copy_out, n, error);
     }));
     return launch_status();
 }

@@ -61,7 +61,7 @@ _SIGNATURES = {
         "chibi_route_by_table": [P, P, I, I, I, L, I, P, P, P],
         "chibi_expert_rows_gemm": [P, I, L, I, I, P, I, P, L, P, L, I, I, I, I, I, I, I, P],
         "chibi_combine_experts": [P, P, P, L, L, I, I, I, F, P],
-        "chibi_layer_end": [P, P, F, P, P, L, I, I, P, P, P, P, I, I, F, P, F, P, I, I, L, I, P, P],
+        "chibi_layer_end": [P, P, F, P, P, L, I, I, P, P, P, P, I, I, F, P, F, P, P, I, I, L, I, P, P],
         "chibi_side_gate": [P, I, L, P, P, I, L, I, I, L, I, I, P, P],
         "chibi_softcap": [P, F, L, P],
         "chibi_zero": [P, L, P],

@@ -190,6 +190,9 @@ class CudaKernels:
         # global scratch to a second kernel that also does what follows the product.
         self.fuse_split_products = True
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        # rows of a tile of the experts' products: the plain kernel's and the tensor-core kernel's
+        self._expert_tile_rows = (int(self.lib.chibi_expert_tile_rows()),
+                                  int(self.lib.chibi_expert_tile_rows_tensor_cores()))
         # the many-row product shares its last, partly filled round of tiles out by K blocks and
         # needs room for one tile of partial sums per SM
         # (one per process, never freed: the library keeps the pointer)
@@ -1189,7 +1192,7 @@ class CudaKernels:
 
     def route_words(self, pairs: int, experts: int) -> int:
         """int32 values of the routing scratch for ``pairs`` (token, choice) pairs."""
-        tile = int(self.lib.chibi_expert_tile_rows())
+        tile = self._expert_tile_rows[0]
         return (experts + 1) + 2 * pairs + 2 * ((pairs + tile - 1) // tile + experts)
 
     def expert_tensor_cores(self, dtype: torch.dtype, hidden: int, inner: int) -> bool:
@@ -1234,7 +1237,7 @@ class CudaKernels:
         self.launches += 4
         fast = interleaved and gate_up.dtype == torch.bfloat16 and self.expert_tensor_cores(x.dtype, D, F) \
             and x.stride(0) % 8 == 0
-        tile = int(self.lib.chibi_expert_tile_rows_tensor_cores() if fast else self.lib.chibi_expert_tile_rows())
+        tile = self._expert_tile_rows[1 if fast else 0]
         flag = 1 if interleaved else 0
         _check(self.lib.chibi_route_by_table(_ptr(tokens), _ptr(table), vocab, top, E, T, tile, _ptr(route),
                                              _ptr(self.error), stream), "routed_experts (route)")
@@ -1250,13 +1253,14 @@ class CudaKernels:
                                               float(weight), stream), "routed_experts (combine)")
 
     def layer_end(self, residual: torch.Tensor, delta: Optional[torch.Tensor], mult: float, side=None,
-                  y_in: Optional[torch.Tensor] = None, norm=None) -> None:
+                  y_in: Optional[torch.Tensor] = None, norm=None, copy_out: Optional[torch.Tensor] = None) -> None:
         """residual += mult * delta; then the per-layer token input, if ``side`` is
         given: (tokens, table [vocab, all], offset, gate [s, n], proj [n, s], norm weight
         [n], activation, eps): y = proj (act(gate x) * table[token, offset:offset + s]),
         x += mult * y / rms(y) * weight -- the two products are done by the kernel unless
         ``y_in`` [T, n] float32 brings y; then, if ``norm`` = (weight, eps, offset, out)
-        is given, out = x / rms(x) * (weight + offset).  One launch, a block per token."""
+        is given, out = x / rms(x) * (weight + offset); ``copy_out`` [T, n] takes the new
+        residual in its own type.  One launch, a block per token."""
         _need_cuda(residual, delta, y_in)
         T, n = residual.shape
         if residual.dtype != torch.float32 or not residual.is_contiguous() or (
@@ -1290,11 +1294,16 @@ class CudaKernels:
             if side is not None and (norm_w.dtype != gate.dtype or float(norm_eps) != float(eps)):
                 raise KernelError("layer_end: the norm's weight type and eps must be the token input's")
             w_type, eps = _code(norm_w), norm_eps
+        if copy_out is not None:
+            _need_cuda(copy_out)
+            if copy_out.shape != (T, n) or not copy_out.is_contiguous() or (out is not None and out.dtype != copy_out.dtype):
+                raise KernelError("layer_end: copy_out is contiguous [T, n], of the norm output's type")
         self.launches += 1
         _check(self.lib.chibi_layer_end(
             _ptr(residual), _ptr(delta), float(mult), _ptr(tokens), _ptr(table), stride, int(offset), vocab, _ptr(gate),
             _ptr(proj), _ptr(side_w), _ptr(y_in), s, kind, float(eps), _ptr(norm_w), float(norm_offset), _ptr(out),
-            _code(out) if out is not None else F32, w_type, T, n, _ptr(self.error), self._stream()), "layer_end")
+            _ptr(copy_out), _code(out) if out is not None else (_code(copy_out) if copy_out is not None else F32),
+            w_type, T, n, _ptr(self.error), self._stream()), "layer_end")
 
     def side_gate(self, gate: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, offset: int, kind: str) -> None:
         """gate[t, j] = act(gate[t, j]) * table[tokens[t], offset + j], in place."""

@@ -94,8 +94,9 @@ class LayerEnd:
         side = ti.kernel_arguments(self.ctx)
         if ti.wants_products(residual.shape[0]):
             # the token input reads the residual after the block's update, so that comes first
-            k.layer_end(residual, self.delta, scale)
-            y = ti.products(residual, self.ctx)
+            x = self.ctx.workspace.get("token_input.x", tuple(residual.shape), b.runtime.dtype)
+            k.layer_end(residual, self.delta, scale, copy_out=x)
+            y = ti.products(x, self.ctx)
             k.layer_end(residual, None, scale, side=side, y_in=y, norm=norm)
         else:
             k.layer_end(residual, self.delta, scale, side=side, norm=norm)

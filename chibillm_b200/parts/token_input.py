@@ -61,13 +61,12 @@ class TokenInput(Part):
         large = tokens > FEW_TOKENS or self.spec.dim * self.spec.hidden_size > SMALL_MATRIX
         return large and getattr(self.runtime.kernels, "side_gate", None) is not None
 
-    def products(self, residual: torch.Tensor, ctx) -> torch.Tensor:
-        """y [T, hidden] float32 = P (act(G x) * e) by matrix products."""
+    def products(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        """y [T, hidden] float32 = P (act(G x) * e) by matrix products; x is the residual in
+        the activations' type."""
         rt, s = self.runtime, self.spec
         k = rt.kernels
-        T = residual.shape[0]
-        x = ctx.workspace.get("token_input.x", (T, s.hidden_size), rt.dtype)
-        k.cast_rows(residual, x)
+        T = x.shape[0]
         g = ctx.workspace.get("token_input.g", (T, s.dim), rt.dtype)
         k.linear(x, self.gate, g)
         k.side_gate(g, ctx.tokens, self.table, s.offset, s.activation)

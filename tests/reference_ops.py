@@ -175,7 +175,7 @@ class ReferenceKernels:
                 total += down[e].float() @ hidden
             acc[t] += weight * total
 
-    def layer_end(self, residual, delta, mult, side=None, y_in=None, norm=None):
+    def layer_end(self, residual, delta, mult, side=None, y_in=None, norm=None, copy_out=None):
         self._count("layer_end")
         if delta is not None:
             residual.add_(mult * delta)
@@ -190,6 +190,8 @@ class ReferenceKernels:
         if norm is not None:
             w, eps, offset, out = norm
             self.rmsnorm(residual, w, eps, offset, out)
+        if copy_out is not None:
+            copy_out.copy_(residual.to(copy_out.dtype))
 
     def side_gate(self, gate, tokens, table, offset, kind):
         e = table[tokens.long(), offset:offset + gate.shape[1]].float()

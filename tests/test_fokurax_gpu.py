@@ -253,8 +253,10 @@ def test_layer_end(kernels, dtype, T, D, side):
     close(out, ref_norm, tol if dtype == "float32" else 1e-2, "layer end, next norm")
     # the update alone, then the token input from y computed outside
     res = x0.clone().to(DEV)
-    kernels.layer_end(res, delta.to(DEV), m)
+    copy = torch.empty(T, D, dtype=wt, device=DEV)
+    kernels.layer_end(res, delta.to(DEV), m, copy_out=copy)
     close(res, x1, 1e-7, "layer end, update only")
+    assert torch.equal(copy, res.to(wt))
     e = w["side.embed"][tokens.long(), layer * side:(layer + 1) * side].double()
     y = ((plain.gelu_tanh(x1 @ w["l1.side.gate"].double().T) * e) @ w["l1.side.proj"].double().T).float()
     kernels.layer_end(res, None, m, side=args, y_in=y.to(DEV))
