@@ -114,7 +114,7 @@ __global__ void heads_rotate_append_kernel(
 // ---------------------------------------------------------------- gated activation with biases
 template <typename TX, typename TW>
 __global__ void gated_activation_kernel(const TX* __restrict__ gate_up, long long stride, const TW* __restrict__ bias,
-                                        TX* __restrict__ out, long long rows, int n, int kind)
+                                        TX* __restrict__ out, long long rows, int n, int kind, int interleaved)
 {
     pdl_enter();
     const long long total = rows * n;
@@ -122,8 +122,11 @@ __global__ void gated_activation_kernel(const TX* __restrict__ gate_up, long lon
          i += (long long)gridDim.x * blockDim.x) {
         const long long r = i / n;
         const int c = (int)(i - r * n);
-        float g = to_f32(gate_up[r * stride + c]);
-        float u = to_f32(gate_up[r * stride + n + c]);
+        // columns: all gates then all ups, or (interleaved) blocks of 16 gates followed by their 16 ups
+        const int gc = interleaved ? (c / 16) * 32 + c % 16 : c;
+        const int uc = interleaved ? gc + 16 : n + c;
+        float g = to_f32(gate_up[r * stride + gc]);
+        float u = to_f32(gate_up[r * stride + uc]);
         if (bias) {
             g += to_f32(bias[c]);
             u += to_f32(bias[n + c]);
@@ -637,15 +640,15 @@ CHIBI_API int chibi_heads_rotate_append(const void* qkv, int x_type, long long q
 }
 
 CHIBI_API int chibi_gated_activation(const void* gate_up, int x_type, long long stride, const void* bias, int w_type,
-                                     void* out, long long rows, int n, int kind, cudaStream_t stream)
+                                     void* out, long long rows, int n, int kind, int interleaved, cudaStream_t stream)
 {
     if (rows <= 0 || n <= 0)
         return CHIBI_OK;
-    if (!gate_up || !out || kind < 0 || kind > 4)
+    if (!gate_up || !out || kind < 0 || kind > 4 || (interleaved && (n % 16 != 0 || bias)))
         return CHIBI_ERR_ARGUMENT;
     CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(w_type, TW, {
         launch(gated_activation_kernel<TX, TW>, dim3(blocks_for(rows * n, 256)), dim3(256), 0, stream,
-               (const TX*)gate_up, stride, (const TW*)bias, (TX*)out, rows, n, kind);
+               (const TX*)gate_up, stride, (const TW*)bias, (TX*)out, rows, n, kind, interleaved);
     }));
     return launch_status();
 }

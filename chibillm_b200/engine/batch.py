@@ -12,7 +12,7 @@ a decode token is an entry of one token.  Metadata is per sequence
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, Hashable, List, Sequence, Tuple
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -95,6 +95,9 @@ class StepContext:
     max_q_len: int = 0
     min_q_len: int = 0
     max_ctx_len: int = 0
+    # the step's token ids on the host (int32 [T]) where the step was packed from ids the host
+    # knows; a part may plan with them (which expert gets how many rows) instead of on the device
+    tokens_host: Optional[torch.Tensor] = None
     # what several layers of this step share: a part computes a value when it first needs it and
     # files it under a key that says what it depends on (a table of rotation angles, cache slots)
     shared: Dict[Hashable, object] = field(default_factory=dict)

@@ -229,7 +229,8 @@ class ModelRunner:
             ctx_len=view("ctx_len", S), state_slots=view("state_slots", S),
             logit_rows=view("logit_rows", R), tables=self.storage.tables, workspace=self.workspace,
             request_ids=[e.request_id for e in entries], q_lens=q_lens, ctx_lens=ctx_lens,
-            slot_list=slots, max_q_len=max(q_lens), min_q_len=min(q_lens), max_ctx_len=max_ctx)
+            slot_list=slots, max_q_len=max(q_lens), min_q_len=min(q_lens), max_ctx_len=max_ctx,
+            tokens_host=host[offsets["tokens"]:offsets["tokens"] + T])
         update_views = {}
         for g, name in enumerate(groups):
             o, cap = info[13 + g], info[13 + G + g]

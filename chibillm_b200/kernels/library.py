@@ -57,7 +57,7 @@ _SIGNATURES = {
         "chibi_reduce_activation": [P, I, L, P, I, I, P],
         "chibi_sample": [P, L, L, I, P, P, P, P, L, P],
         "chibi_heads_rotate_append": [P, I, L, P, P, P, I, P, F, P, P, P, P, I, L, I, I, I, I, I, I, I, F, I, I, P, P],
-        "chibi_gated_activation": [P, I, L, P, I, P, L, I, I, P],
+        "chibi_gated_activation": [P, I, L, P, I, P, L, I, I, I, P],
         "chibi_route_by_table": [P, P, I, I, I, L, I, P, P, P],
         "chibi_expert_rows_gemm": [P, I, L, I, I, P, I, P, L, P, L, I, I, I, I, I, I, I, P],
         "chibi_combine_experts": [P, P, P, L, L, I, I, I, F, P],

@@ -1175,8 +1175,9 @@ class CudaKernels:
             "heads_rotate_append")
 
     def gated_activation(self, gate_up: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-                         kind: str) -> None:
-        """out = act(gate + b_gate) * (up + b_up); gate_up [T, 2 n] (gate columns first),
+                         kind: str, interleaved: bool = False) -> None:
+        """out = act(gate + b_gate) * (up + b_up); gate_up [T, 2 n] (gate columns first, or,
+        ``interleaved``, blocks of 16 gate columns each followed by its 16 up columns),
         bias [2 n] or None."""
         _need_cuda(gate_up, bias, out)
         _rows_contiguous(gate_up, "gated_activation: gate_up")
@@ -1188,7 +1189,8 @@ class CudaKernels:
         self.launches += 1
         _check(self.lib.chibi_gated_activation(_ptr(gate_up), _code(gate_up), gate_up.stride(0), _ptr(bias),
                                                _code(bias) if bias is not None else F32, _ptr(out), T, n,
-                                               self.ACTIVATIONS[kind], self._stream()), "gated_activation")
+                                               self.ACTIVATIONS[kind], 1 if interleaved else 0, self._stream()),
+               "gated_activation")
 
     def route_words(self, pairs: int, experts: int) -> int:
         """int32 values of the routing scratch for ``pairs`` (token, choice) pairs."""
@@ -1251,6 +1253,21 @@ class CudaKernels:
             self.tensor_core_calls += 2
         _check(self.lib.chibi_combine_experts(_ptr(y), _ptr(route), _ptr(acc), acc.stride(0), T, D, top, E,
                                               float(weight), stream), "routed_experts (combine)")
+
+    def combine_experts(self, y: torch.Tensor, route: torch.Tensor, acc: torch.Tensor, top: int, experts: int,
+                        weight: float) -> None:
+        """acc[t] += weight * sum over the token's choices s (in their order) of
+        y[row_of_pair[t top + s]]; ``route`` is laid out as ``routed_experts`` lays it out
+        (offsets [experts + 1] | pair_of_row [pairs] | row_of_pair [pairs] | ...)."""
+        _need_cuda(y, route, acc)
+        T, D = acc.shape
+        if y.shape != (T * top, D) or y.dtype != torch.float32 or not y.is_contiguous() or acc.dtype != torch.float32 \
+                or route.dtype != torch.int32 or route.numel() < experts + 1 + 2 * T * top:
+            raise KernelError("combine_experts: shapes or types")
+        _rows_contiguous(acc, "combine_experts: acc")
+        self.launches += 1
+        _check(self.lib.chibi_combine_experts(_ptr(y), _ptr(route), _ptr(acc), acc.stride(0), T, D, top, experts,
+                                              float(weight), self._stream()), "combine_experts")
 
     def layer_end(self, residual: torch.Tensor, delta: Optional[torch.Tensor], mult: float, side=None,
                   y_in: Optional[torch.Tensor] = None, norm=None, copy_out: Optional[torch.Tensor] = None) -> None:

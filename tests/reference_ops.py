@@ -154,8 +154,18 @@ class ReferenceKernels:
         self.activation(t, kind)
         return t
 
-    def gated_activation(self, gate_up, bias, out, kind):
+    def combine_experts(self, y, route, acc, top, experts, weight):
+        self._count("combine_experts")
+        T = acc.shape[0]
+        rows = route[experts + 1 + T * top:experts + 1 + 2 * T * top].long().view(T, top)
+        total = torch.zeros_like(acc)
+        for s in range(top):
+            total += y[rows[:, s]]
+        acc.add_(weight * total)
+
+    def gated_activation(self, gate_up, bias, out, kind, interleaved=False):
         self._count("gated_activation")
+        assert not interleaved
         n = out.shape[1]
         gu = gate_up.float() + (bias.float() if bias is not None else 0.0)
         out.copy_((self._act(gu[:, :n], kind) * gu[:, n:]).to(out.dtype))

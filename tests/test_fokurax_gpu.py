@@ -180,6 +180,14 @@ def test_gated_activation_with_biases(kernels, dtype, kind):
         out = torch.empty(T, n, dtype=dt, device=DEV)
         kernels.gated_activation(gate_up.to(DEV), b.to(DEV) if b is not None else None, out, kind)
         close(out, ref, 1e-6 if dtype == "float32" else 1e-2, f"gated activation {kind}")
+    # blocks of 16 gate columns, each followed by its 16 up columns
+    n = 48
+    gate_up = (torch.randn(T, 2 * n, generator=g) * 2).to(dt)
+    blocks = gate_up.double().view(T, n // 16, 2, 16)
+    ref = act(blocks[:, :, 0].reshape(T, n)) * blocks[:, :, 1].reshape(T, n)
+    out = torch.empty(T, n, dtype=dt, device=DEV)
+    kernels.gated_activation(gate_up.to(DEV), None, out, kind, interleaved=True)
+    close(out, ref, 1e-6 if dtype == "float32" else 1e-2, f"gated activation {kind}, interleaved")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -341,6 +349,22 @@ def test_cutting_and_batching(folders, expected, case, dtype):
     helpers.assert_logits_close(got, mixed_ref, tol, f"fokurax {case} {dtype} mixed")
     runner2.cache.check_invariants()
     assert not runner2.cache.requests
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_experts_sorted_on_the_host(folders, expected, dtype, monkeypatch):
+    """Prompt steps whose experts are sorted on the host and run one after the other
+    through the ordinary products (what large experts do), on a small model."""
+    from chibillm_b200.parts.mlp import TableExperts
+    monkeypatch.setattr(TableExperts, "MANY_PAIRS", 4)
+    monkeypatch.setattr(TableExperts, "MUCH_WORK", 0)
+    reqs, ref, mixed_reqs, mixed_ref = expected["F3"]
+    runner = make_runner(folders["F3"], dtype, 16, 448)
+    before = runner.runtime.kernels.launches
+    got = helpers.run_trace(runner, helpers.trace_portions(reqs, seed=4))
+    helpers.assert_logits_close(got, ref, helpers.TOL[dtype], f"fokurax F3 {dtype} experts sorted on the host")
+    got = helpers.run_trace(make_runner(folders["F3"], dtype, 16, 640), helpers.trace_mixed(mixed_reqs, 640, seed=6))
+    helpers.assert_logits_close(got, mixed_ref, helpers.TOL[dtype], f"fokurax F3 {dtype} experts sorted on the host, mixed")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -248,3 +248,23 @@ def test_command_line_and_scheduler_on_cpu(tmp_path):
             top = torch.topk(row, 2).values
             if float(top[0] - top[1]) > 1e-4 * float(row.abs().max()):
                 assert int(torch.argmax(row)) == tok
+
+
+def test_experts_sorted_on_the_host_agree_with_the_device_plan(tmp_path, monkeypatch):
+    """Prompt steps of many (token, choice) pairs are sorted by expert on the host and go
+    expert by expert through the ordinary products: same logits as the plan made on the
+    device, in whole prompts and in portions (a portion of one token takes the other way)."""
+    from chibillm_b200.parts.mlp import TableExperts
+    cfg = fokurax_models.get("F1")
+    folder = fokurax_models.write_model(cfg, str(tmp_path / "f1"), seed=7)
+    reqs = helpers.random_requests(cfg["vocab"], [40, 9], seed=3)
+    ref = fokurax_models.plain_logits(cfg, 7, reqs)
+    monkeypatch.setattr(TableExperts, "MANY_PAIRS", 4)
+    monkeypatch.setattr(TableExperts, "MUCH_WORK", 0)
+    runner = cpu_runner(folder, 4, 64)
+    for trace, what in ((helpers.trace_whole(reqs), "whole"), (helpers.trace_portions(reqs, seed=1), "portions"),
+                        (helpers.trace_last_decoded(reqs, 5), "decoded")):
+        got = helpers.run_trace(runner, trace)
+        helpers.assert_logits_close(got, ref, helpers.TOL["float32"], f"fokurax experts sorted on the host, {what}")
+    calls = runner.runtime.kernels.calls
+    assert calls.get("combine_experts", 0) > 0 and calls.get("routed_experts", 0) > 0
