@@ -290,12 +290,18 @@ expert_rows_gemm_kernel(const TA* __restrict__ a, long long a_stride, const int*
 }
 
 // The same product on the tensor cores (bfloat16, 32-bit sums): tiles of 128 rows of one expert
-// times 128 columns, K in blocks of 32 through three stages of cp.async, eight warps of 64 x 32
-// sums each (mma.sync m16n8k16).  Rows that a tile does not have are filled with zeros and not
+// times 128 columns, K in blocks of 32 through four stages of cp.async, eight warps of 64 x 32
+// sums each (mma.sync m16n8k16), two CTAs to an SM (82 KB of shared memory and at most 128 registers
+// each; with K blocks of 64 and three stages only one CTA fitted, and its eight warps hid too little:
+// 44 % of the tensor pipe cycles, 12 % of the warp slots; 218 -> 242 TFLOP/s at 4,096 rows of 8 experts
+// of 2,048 x 3,072).  For a decode step's few rows a kernel with a warp to a column that streams the
+// weight rows with plain loads was measured too and was slower (135 to 145 us against 112 to 125 for 7
+// experts of that size): every block first walks tile map -> offsets -> row index -> row, four dependent
+// trips, for 64 KB of weights; it is not kept.  Rows that a tile does not have are filled with zeros and not
 // stored, so a decode step's tiles of one or two rows stream their expert's weights once.
 // GATED: the expert's matrix holds blocks of 16 gate rows followed by their 16 up rows, so a
 // warp's 32 columns are 16 gate sums and the 16 up sums that belong to them, in the same lanes.
-constexpr int TG_M = 128, TG_N = 128, TG_K = 32, TG_PAD = 40, TG_STAGES = 3;
+constexpr int TG_M = 128, TG_N = 128, TG_K = 32, TG_PAD = 40, TG_STAGES = 4;
 
 __device__ __forceinline__ void tg_cp_async16(void* dst, const void* src, bool valid)
 {
@@ -319,7 +325,7 @@ __device__ __forceinline__ void tg_mma_bf16(float (&c)[4], const uint32_t (&a)[4
 }
 
 template <bool GATED>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 expert_rows_mma_kernel(const __nv_bfloat16* __restrict__ a, long long a_stride, const int* __restrict__ a_index,
                        int a_div, const __nv_bfloat16* __restrict__ w, long long w_expert_stride, void* __restrict__ out,
                        long long out_stride, const int* __restrict__ offsets, const int* __restrict__ tile_expert,
