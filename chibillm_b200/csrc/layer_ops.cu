@@ -135,6 +135,43 @@ __global__ void gated_activation_kernel(const TX* __restrict__ gate_up, long lon
     }
 }
 
+// The same for bfloat16 rows whose sizes and addresses allow 16-byte accesses: a thread takes 8
+// neighbouring columns (a run of 8 never crosses a block of 16 interleaved columns).
+template <typename TW>
+__global__ void gated_activation_vec8_kernel(const __nv_bfloat16* __restrict__ gate_up, long long stride,
+                                             const TW* __restrict__ bias, __nv_bfloat16* __restrict__ out,
+                                             long long rows, int n, int kind, int interleaved)
+{
+    pdl_enter();
+    const int groups = n / 8;
+    const long long total = rows * groups;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / groups;
+        const int c = (int)(i - r * groups) * 8;
+        const int gc = interleaved ? (c / 16) * 32 + c % 16 : c;
+        const int uc = interleaved ? gc + 16 : n + c;
+        const uint4 graw = *reinterpret_cast<const uint4*>(gate_up + r * stride + gc);
+        const uint4 uraw = *reinterpret_cast<const uint4*>(gate_up + r * stride + uc);
+        const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&graw);
+        const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+        uint4 oraw;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&oraw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float2 g = __bfloat1622float2(gh[j]), u = __bfloat1622float2(uh[j]);
+            if (bias) {
+                g.x += to_f32(bias[c + 2 * j]);
+                g.y += to_f32(bias[c + 2 * j + 1]);
+                u.x += to_f32(bias[n + c + 2 * j]);
+                u.y += to_f32(bias[n + c + 2 * j + 1]);
+            }
+            oh[j] = __floats2bfloat162_rn(activate(g.x, kind) * u.x, activate(g.y, kind) * u.y);
+        }
+        *reinterpret_cast<uint4*>(out + r * n + c) = oraw;
+    }
+}
+
 // ---------------------------------------------------------------- experts chosen by a table
 // One block.  pairs = tokens * top; pair p = token p / top, choice p % top.  Writes
 // offsets[experts + 1], pair_of_row[pairs] (rows sorted by expert), row_of_pair[pairs],
@@ -652,6 +689,15 @@ CHIBI_API int chibi_gated_activation(const void* gate_up, int x_type, long long 
         return CHIBI_OK;
     if (!gate_up || !out || kind < 0 || kind > 4 || (interleaved && (n % 16 != 0 || bias)))
         return CHIBI_ERR_ARGUMENT;
+    if (x_type == CHIBI_BF16 && n % 8 == 0 && stride % 8 == 0 && (reinterpret_cast<uintptr_t>(gate_up) & 15) == 0
+        && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        CHIBI_DISPATCH_TYPE(w_type, TW, {
+            launch(gated_activation_vec8_kernel<TW>, dim3(blocks_for(rows * (n / 8), 256)), dim3(256), 0, stream,
+                   (const __nv_bfloat16*)gate_up, stride, (const TW*)bias, (__nv_bfloat16*)out, rows, n, kind,
+                   interleaved);
+        });
+        return launch_status();
+    }
     CHIBI_DISPATCH_TYPE(x_type, TX, CHIBI_DISPATCH_TYPE(w_type, TW, {
         launch(gated_activation_kernel<TX, TW>, dim3(blocks_for(rows * n, 256)), dim3(256), 0, stream,
                (const TX*)gate_up, stride, (const TW*)bias, (TX*)out, rows, n, kind, interleaved);
