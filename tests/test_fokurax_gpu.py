@@ -164,6 +164,27 @@ def test_attention_sees_its_block_and_nothing_before(kernels, dtype, d):
     assert float((free[T - 1] - ref[T - 1]).abs().max()) > 0.1
 
 
+@pytest.mark.parametrize("chunk", [1024, 300, 4096])
+@pytest.mark.parametrize("d", [64, 128])
+def test_a_short_portion_after_a_long_context(kernels, d, chunk):
+    """A portion of 110 tokens after 1,990: the tcgen05 prompt kernel cuts the keys of its few
+    rows into ranges for several CTAs and merges them.  With blocks of 1,024 the rows' keys
+    begin inside the context, with blocks of 300 most ranges are empty, with blocks of 4,096
+    nothing is cut off; then single tokens (the split-key decode kernel) from 2,100 on."""
+    H, G, T, page_size = 4, 1, 2110, 16
+    g = torch.Generator().manual_seed(chunk + d)
+    q = torch.randn(T, H, d, generator=g).bfloat16()
+    k = torch.randn(T, G, d, generator=g).bfloat16()
+    v = torch.randn(T, G, d, generator=g).bfloat16()
+    rot = fokurax_models.rot(d // 2, 10000.0, 8.0, original=256)
+    scale, eps = 4.0 / math.sqrt(d), 1e-5
+    ref, _ = attention_reference(q, k, v, rot, eps, scale, chunk)
+    cuts = [(0, 1990), (1990, 2100)] + [(i, i + 1) for i in range(2100, T)]
+    got, _ = run_attention(kernels, q, k, v, rot, eps, scale, chunk, "bfloat16", page_size, cuts)
+    close(got[1990:], ref[1990:], 2e-2, "a short portion and single tokens after a long context")
+    close(got, ref, 2e-2, "all rows")
+
+
 # ------------------------------------------------------------------ feed-forwards
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("kind", ["gelu_tanh", "silu"])
