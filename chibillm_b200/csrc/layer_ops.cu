@@ -175,13 +175,14 @@ __global__ void gated_activation_vec8_kernel(const __nv_bfloat16* __restrict__ g
 // ---------------------------------------------------------------- experts chosen by a table
 // One block.  pairs = tokens * top; pair p = token p / top, choice p % top.  Writes
 // offsets[experts + 1], pair_of_row[pairs] (rows sorted by expert), row_of_pair[pairs],
-// and the tile map: tile_expert[max_tiles] (-1: unused), tile_row0[max_tiles], every tile
-// holding up to tile_rows rows of one expert.  max_tiles = ceil(pairs / tile_rows) + experts.
+// the tile map: tile_expert[max_tiles] (-1: unused), tile_row0[max_tiles], every tile
+// holding up to tile_rows rows of one expert (max_tiles = ceil(pairs / tile_rows) + experts),
+// and token_of_row[pairs] (which row of the tokens' array every sorted row reads).
 __global__ void __launch_bounds__(1024)
 route_by_table_kernel(const int* __restrict__ tokens, const int* __restrict__ table, int vocab, int top, int experts,
                       int num_tokens, int tile_rows, int max_tiles, int* __restrict__ offsets,
                       int* __restrict__ pair_of_row, int* __restrict__ row_of_pair, int* __restrict__ tile_expert,
-                      int* __restrict__ tile_row0, int* __restrict__ error)
+                      int* __restrict__ tile_row0, int* __restrict__ token_of_row, int* __restrict__ error)
 {
     pdl_enter();
     extern __shared__ int counts[];                    // [experts] counts, then [experts] cursors
@@ -230,6 +231,7 @@ route_by_table_kernel(const int* __restrict__ tokens, const int* __restrict__ ta
         const int r = atomicAdd(&cursor[e], 1);
         pair_of_row[r] = p;
         row_of_pair[p] = r;
+        token_of_row[r] = p / top;
     }
 }
 
@@ -705,8 +707,9 @@ CHIBI_API int chibi_gated_activation(const void* gate_up, int x_type, long long 
     return launch_status();
 }
 
-// route: int32 scratch of (experts + 1) + 2 pairs + 2 max_tiles values (max_tiles = ceil(pairs / chibi_expert_tile_rows()) + experts), laid out as
-// offsets[experts + 1] | pair_of_row[pairs] | row_of_pair[pairs] | tile_expert[max_tiles] | tile_row0[max_tiles]
+// route: int32 scratch of (experts + 1) + 3 pairs + 2 max_tiles values (max_tiles = ceil(pairs / chibi_expert_tile_rows()) + experts), laid out as
+// offsets[experts + 1] | pair_of_row[pairs] | row_of_pair[pairs] | tile_expert[max_tiles] | tile_row0[max_tiles] |
+// token_of_row[pairs]
 CHIBI_API int chibi_expert_tile_rows() { return EG_M; }
 CHIBI_API int chibi_expert_tile_rows_tensor_cores() { return TG_M; }
 
@@ -728,7 +731,7 @@ CHIBI_API int chibi_route_by_table(const int* tokens, const int* table, int voca
     int* tile_row0 = tile_expert + max_tiles;
     launch(route_by_table_kernel, dim3(1), dim3(1024), (size_t)2 * experts * sizeof(int), stream, tokens, table, vocab,
            top, experts, (int)num_tokens, tile_rows, max_tiles, offsets, pair_of_row, row_of_pair, tile_expert, tile_row0,
-           error);
+           tile_row0 + max_tiles, error);
     return launch_status();
 }
 

@@ -66,6 +66,7 @@ _SIGNATURES = {
         "chibi_softcap": [P, F, L, P],
         "chibi_zero": [P, L, P],
         "chibi_expert_tile_rows": [],
+        "chibi_expert_rows_tc": [P, P, P, L, P, L, I, I, I, I, I, P, P],
         "chibi_expert_tile_rows_tensor_cores": [],
     },
     "chibi_attention_tc": {

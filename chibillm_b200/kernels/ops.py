@@ -1195,12 +1195,22 @@ class CudaKernels:
     def route_words(self, pairs: int, experts: int) -> int:
         """int32 values of the routing scratch for ``pairs`` (token, choice) pairs."""
         tile = self._expert_tile_rows[0]
-        return (experts + 1) + 2 * pairs + 2 * ((pairs + tile - 1) // tile + experts)
+        return (experts + 1) + 3 * pairs + 2 * ((pairs + tile - 1) // tile + experts)
+
+    # from so many (token, choice) pairs on the experts' products run on tcgen05 (tiles of 128 rows are
+    # computed whole there; the mma.sync kernel skips the empty row blocks of a decode step's tiles)
+    EXPERTS_TCGEN05_MIN_PAIRS = 256
+    use_tcgen05_experts = True
 
     def expert_tensor_cores(self, dtype: torch.dtype, hidden: int, inner: int) -> bool:
         """Whether ``routed_experts`` runs experts of these sizes on the tensor cores; their
         gate | up matrices are then to be stacked with ``interleave_expert_gate_up``."""
         return self.use_tensor_cores and dtype == torch.bfloat16 and hidden % 32 == 0 and inner % 32 == 0
+
+    def experts_on_tcgen05(self, dtype: torch.dtype, hidden: int, inner: int) -> bool:
+        """Whether ``routed_experts`` runs the products of many rows of such experts on tcgen05."""
+        return self.expert_tensor_cores(dtype, hidden, inner) and hidden % 64 == 0 and inner % 64 == 0 \
+            and self.use_tcgen05_experts
 
     @staticmethod
     def interleave_expert_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -1210,7 +1220,8 @@ class CudaKernels:
 
     def routed_experts(self, x: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, gate_up: torch.Tensor,
                        down: torch.Tensor, acc: torch.Tensor, route: torch.Tensor, act: torch.Tensor,
-                       y: torch.Tensor, kind: str, weight: float, interleaved: bool = False) -> None:
+                       y: torch.Tensor, kind: str, weight: float, interleaved: bool = False,
+                       sorted_x: Optional[torch.Tensor] = None) -> None:
         """acc[t] += weight * sum over the experts that ``table[tokens[t]]`` names (in the
         table's order) of down_e (act(gate_e x[t]) * (up_e x[t])).  gate_up [E, 2 F, D]
         (gate rows first), down [E, D, F], table int32 [vocab, top]; scratch: route int32
@@ -1218,7 +1229,9 @@ class CudaKernels:
         launches; nothing is read on the host.  ``interleaved``: gate_up's experts hold
         blocks of 16 gate rows and their 16 up rows (``interleave_expert_gate_up``); with
         bfloat16 and sizes that are multiples of 32 the products then run on the tensor
-        cores."""
+        cores: with ``sorted_x`` (scratch [T top, D] in x's type), sizes that are multiples
+        of 64 and ``EXPERTS_TCGEN05_MIN_PAIRS`` pairs or more on tcgen05 (the rows are first
+        copied into sorted order, which TMA needs), else with ``mma.sync``."""
         _need_cuda(x, tokens, table, gate_up, down, acc, route, act, y)
         _rows_contiguous(x, "routed_experts: x")
         _rows_contiguous(acc, "routed_experts: acc")
@@ -1243,6 +1256,26 @@ class CudaKernels:
         flag = 1 if interleaved else 0
         _check(self.lib.chibi_route_by_table(_ptr(tokens), _ptr(table), vocab, top, E, T, tile, _ptr(route),
                                              _ptr(self.error), stream), "routed_experts (route)")
+        if fast and sorted_x is not None and pairs >= self.EXPERTS_TCGEN05_MIN_PAIRS \
+                and self.experts_on_tcgen05(x.dtype, D, F):
+            _need_cuda(sorted_x)
+            if sorted_x.shape != (pairs, D) or sorted_x.dtype != x.dtype or not sorted_x.is_contiguous() \
+                    or not x.is_contiguous():
+                raise KernelError("routed_experts: sorted_x is contiguous [T top, D] of x's type")
+            max_tiles = (pairs + tile - 1) // tile + E
+            rows = route[E + 1 + 2 * pairs + 2 * max_tiles:E + 1 + 3 * pairs + 2 * max_tiles]
+            self.gather_rows(x, rows, sorted_x)
+            s1 = self.lib.chibi_expert_rows_tc(_ptr(sorted_x), _ptr(gate_up), _ptr(act), F, _ptr(route), pairs, E,
+                                               2 * F, D, 1, self.ACTIVATIONS[kind], _ptr(self.error), stream)
+            if s1 == 0:
+                _check(self.lib.chibi_expert_rows_tc(_ptr(act), _ptr(down), _ptr(y), D, _ptr(route), pairs, E, D, F, 0,
+                                                     0, _ptr(self.error), stream), "routed_experts (down, tcgen05)")
+                _check(self.lib.chibi_combine_experts(_ptr(y), _ptr(route), _ptr(acc), acc.stride(0), T, D, top, E,
+                                                      float(weight), stream), "routed_experts (combine)")
+                self.tensor_core_calls += 2
+                return
+            if s1 != -2:
+                _check(s1, "routed_experts (gate | up, tcgen05)")
         _check(self.lib.chibi_expert_rows_gemm(_ptr(x), _code(x), x.stride(0), 1, top, _ptr(gate_up), _code(gate_up),
                                                _ptr(act), F, _ptr(route), pairs, E, F, D, 1, self.ACTIVATIONS[kind],
                                                tile, flag, stream), "routed_experts (gate | up)")

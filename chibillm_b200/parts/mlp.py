@@ -186,12 +186,13 @@ class TableExperts(FeedForward):
     def launch_key(self, ctx):
         return ()
 
-    # A prompt step whose token ids the host knows, of so many (token, choice) pairs and of so many
-    # multiplications per expert on average, is sorted by expert on the host, and every expert's rows go
-    # through the kernels' ordinary matrix products (2 E launches instead of 2: smaller experts lose more
-    # to the launches than the faster product gains; measured at 8 experts and 4,096 pairs: width 1,024,
+    # Experts whose sizes the tcgen05 kernel of the routed rows does not take (no multiples of 64): a prompt
+    # step whose token ids the host knows, of so many (token, choice) pairs and of so many multiplications
+    # per expert on average, is sorted by expert on the host, and every expert's rows go through the kernels'
+    # ordinary matrix products (2 E launches instead of 2: smaller experts lose more to the launches than the
+    # faster product gains; measured against the mma.sync kernel at 8 experts and 4,096 pairs: width 1,024,
     # ff 1,536: 2.1 -> 3.6 ms a prompt step; width 2,048, ff 3,072: 4.5 -> 3.7; width 4,096, ff 6,144:
-    # 13.0 -> 6.8)
+    # 13.0 -> 6.8; the tcgen05 kernel takes 1.6, 2.7 and 6.6 and is used wherever it can be)
     MANY_PAIRS = 512
     MUCH_WORK = 1 << 31
 
@@ -236,13 +237,19 @@ class TableExperts(FeedForward):
         pairs = T * s.top
         if pairs >= self.MANY_PAIRS and ctx.max_q_len > 1 and getattr(ctx, "tokens_host", None) is not None \
                 and pairs * s.intermediate_size * s.hidden_size >= self.MUCH_WORK * s.num_experts \
-                and getattr(k, "combine_experts", None) is not None:
+                and getattr(k, "combine_experts", None) is not None \
+                and not (hasattr(k, "experts_on_tcgen05")
+                         and k.experts_on_tcgen05(self.runtime.dtype, s.hidden_size, s.intermediate_size)):
             return self._forward_expert_by_expert(x, residual, ctx)
         route = ctx.workspace.get("experts.route", (k.route_words(pairs, s.num_experts),), torch.int32)
         act = ctx.workspace.get("experts.act", (pairs, s.intermediate_size), self.runtime.dtype)
         y = ctx.workspace.get("experts.out", (pairs, s.hidden_size), torch.float32)
+        extra = {}
+        if self.interleaved:
+            extra = {"interleaved": True,
+                     "sorted_x": ctx.workspace.get("experts.sorted", (pairs, s.hidden_size), self.runtime.dtype)}
         k.routed_experts(x, ctx.tokens, self.table, self.gate_up, self.down, residual, route, act, y,
-                         s.activation, 1.0 / s.top, **({"interleaved": True} if self.interleaved else {}))
+                         s.activation, 1.0 / s.top, **extra)
         return None
 
 

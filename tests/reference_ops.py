@@ -173,7 +173,8 @@ class ReferenceKernels:
     def route_words(self, pairs, experts):
         return 1
 
-    def routed_experts(self, x, tokens, table, gate_up, down, acc, route, act, y, kind, weight, interleaved=False):
+    def routed_experts(self, x, tokens, table, gate_up, down, acc, route, act, y, kind, weight, interleaved=False,
+                       sorted_x=None):
         assert not interleaved
         self._count("routed_experts")
         F = down.shape[2]

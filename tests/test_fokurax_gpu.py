@@ -215,11 +215,13 @@ def test_gated_activation_with_biases(kernels, dtype, kind):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("T,D,F,E,top", [(1, 64, 40, 5, 2), (9, 96, 24, 3, 3), (300, 80, 100, 7, 1), (700, 128, 64, 4, 2),
                                          (33, 72, 130, 12, 5), (3, 96, 32, 6, 2), (1000, 160, 96, 5, 3),
-                                         (130, 256, 224, 3, 1), (70, 192, 128, 4, 2), (5, 256, 320, 9, 3)])
+                                         (130, 256, 224, 3, 1), (70, 192, 128, 4, 2), (5, 256, 320, 9, 3),
+                                         (300, 192, 128, 5, 3), (2048, 256, 192, 8, 2)])
 def test_experts_chosen_by_a_table(kernels, dtype, T, D, F, E, top):
     """Few tokens (every tile holds a row or two), many (several tiles an expert), sizes
     that end inside a tile, tokens that repeat, experts that nobody uses.  With sizes that
-    are multiples of 32 the bfloat16 runs take the tensor-core kernel, else the plain one."""
+    are multiples of 32 the bfloat16 runs take the tensor-core kernels (multiples of 64 and 256
+    pairs or more: tcgen05, and once more with that switched off: mma.sync), else the plain one."""
     g = torch.Generator().manual_seed(T + E)
     dt = DTYPES[dtype]
     V = 50
@@ -243,14 +245,22 @@ def test_experts_chosen_by_a_table(kernels, dtype, T, D, F, E, top):
         gate_up = torch.stack([torch.cat([w[f"m.e{e}.gate"], w[f"m.e{e}.up"]]) for e in range(E)]).to(DEV)
     down = torch.stack([w[f"m.e{e}.down"] for e in range(E)]).to(DEV)
     start = torch.randn(T, D, generator=g)
-    acc = start.clone().to(DEV)
     route = torch.empty(kernels.route_words(T * top, E), dtype=torch.int32, device=DEV)
     act = torch.empty(T * top, F, dtype=dt, device=DEV)
     y = torch.empty(T * top, D, dtype=torch.float32, device=DEV)
-    kernels.routed_experts(x.to(DEV), tokens.to(DEV), table.to(DEV), gate_up, down, acc, route, act, y, "silu", 1.0 / top,
-                           interleaved=fast)
-    kernels.check_error_word()
-    close(acc.cpu() - start, ref, 2e-5 if dtype == "float32" else 2e-2, "experts")
+    sorted_x = torch.empty(T * top, D, dtype=dt, device=DEV) if fast else None
+    for tcgen05 in ((True, False) if fast else (True,)):
+        kernels.use_tcgen05_experts = tcgen05
+        try:
+            acc = start.clone().to(DEV)
+            act.fill_(float("nan"))
+            y.fill_(float("nan"))
+            kernels.routed_experts(x.to(DEV), tokens.to(DEV), table.to(DEV), gate_up, down, acc, route, act, y, "silu",
+                                   1.0 / top, interleaved=fast, sorted_x=sorted_x)
+            kernels.check_error_word()
+        finally:
+            kernels.use_tcgen05_experts = True
+        close(acc.cpu() - start, ref, 2e-5 if dtype == "float32" else 2e-2, f"experts (tcgen05 {tcgen05})")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -376,16 +386,19 @@ def test_cutting_and_batching(folders, expected, case, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_experts_sorted_on_the_host(folders, expected, dtype, monkeypatch):
     """Prompt steps whose experts are sorted on the host and run one after the other
-    through the ordinary products (what large experts do), on a small model."""
+    through the ordinary products (what large experts of sizes that the tcgen05 kernel of
+    the routed rows does not take do), on a small model with that kernel switched off."""
     from chibillm_b200.parts.mlp import TableExperts
     monkeypatch.setattr(TableExperts, "MANY_PAIRS", 4)
     monkeypatch.setattr(TableExperts, "MUCH_WORK", 0)
     reqs, ref, mixed_reqs, mixed_ref = expected["F3"]
     runner = make_runner(folders["F3"], dtype, 16, 448)
-    before = runner.runtime.kernels.launches
+    runner.runtime.kernels.use_tcgen05_experts = False
     got = helpers.run_trace(runner, helpers.trace_portions(reqs, seed=4))
     helpers.assert_logits_close(got, ref, helpers.TOL[dtype], f"fokurax F3 {dtype} experts sorted on the host")
-    got = helpers.run_trace(make_runner(folders["F3"], dtype, 16, 640), helpers.trace_mixed(mixed_reqs, 640, seed=6))
+    runner = make_runner(folders["F3"], dtype, 16, 640)
+    runner.runtime.kernels.use_tcgen05_experts = False
+    got = helpers.run_trace(runner, helpers.trace_mixed(mixed_reqs, 640, seed=6))
     helpers.assert_logits_close(got, mixed_ref, helpers.TOL[dtype], f"fokurax F3 {dtype} experts sorted on the host, mixed")
 
 
