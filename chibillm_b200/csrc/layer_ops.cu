@@ -11,7 +11,8 @@
 //   per token id from a table.  The (token, choice) pairs are sorted by expert on the
 //   device, the products run as tiles of rows that belong to one expert each (the tile
 //   map is made by the sorting kernel, so nothing is read on the host), and the chosen
-//   experts' outputs are added in the order of the choices.
+//   experts' outputs are added in the order of the choices.  (The products of sizes that
+//   are multiples of 64 run on tcgen05 from the same map: experts_tcgen05.cu.)
 // * layer_end: residual += m * delta, then the per-layer token input
 //   (y = P (act(G x) * e[token]); x += m * y / rms(y) * w), then, if asked, the next
 //   norm's output.  The products with G and P are done here for few tokens, or taken

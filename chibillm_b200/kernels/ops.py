@@ -454,6 +454,9 @@ class CudaKernels:
                     18: "a wait that ran out (matrix product by pairs of CTAs: tensor-core issuer)",
                     19: "a wait that ran out (matrix product by pairs of CTAs: epilogue)",
                     20: "a wait that ran out (matrix product by pairs of CTAs: accumulator hand-over)",
+                    31: "a wait that ran out (experts' product: loader)",
+                    32: "a wait that ran out (experts' product: tensor-core issuer)",
+                    33: "a wait that ran out (experts' product: epilogue)",
                     **{c: f"a wait that ran out (tcgen05 attention, point {c})" for c in range(21, 30)}}.get(code, f"code {code}")
             raise KernelError(f"a kernel refused {what}")
 
@@ -1197,9 +1200,11 @@ class CudaKernels:
         tile = self._expert_tile_rows[0]
         return (experts + 1) + 3 * pairs + 2 * ((pairs + tile - 1) // tile + experts)
 
-    # from so many (token, choice) pairs on the experts' products run on tcgen05 (tiles of 128 rows are
-    # computed whole there; the mma.sync kernel skips the empty row blocks of a decode step's tiles)
-    EXPERTS_TCGEN05_MIN_PAIRS = 256
+    # from so many (token, choice) pairs on the experts' products run on tcgen05.  Its tiles of 128 rows
+    # are computed whole, also for a decode step's one or two rows, while the mma.sync kernel skips empty
+    # row blocks; streaming the weights by TMA wins all the same (8 and 64 tokens, 8 experts of
+    # 2,048 x 3,072: 125 / 135 -> 103 / 89 us; of 4,096 x 6,144: 305 / 350 -> 209 / 227 us)
+    EXPERTS_TCGEN05_MIN_PAIRS = 1
     use_tcgen05_experts = True
 
     def expert_tensor_cores(self, dtype: torch.dtype, hidden: int, inner: int) -> bool:
@@ -1230,8 +1235,8 @@ class CudaKernels:
         blocks of 16 gate rows and their 16 up rows (``interleave_expert_gate_up``); with
         bfloat16 and sizes that are multiples of 32 the products then run on the tensor
         cores: with ``sorted_x`` (scratch [T top, D] in x's type), sizes that are multiples
-        of 64 and ``EXPERTS_TCGEN05_MIN_PAIRS`` pairs or more on tcgen05 (the rows are first
-        copied into sorted order, which TMA needs), else with ``mma.sync``."""
+        of 64 on tcgen05 (the rows are first copied into sorted order, which TMA needs), else
+        with ``mma.sync``."""
         _need_cuda(x, tokens, table, gate_up, down, acc, route, act, y)
         _rows_contiguous(x, "routed_experts: x")
         _rows_contiguous(acc, "routed_experts: acc")
