@@ -400,7 +400,7 @@ def fokurax_config(width, heads, kv_heads, dim, ff, vocab=32768):
     token, so every layer does the arithmetic of a dense one; attention in blocks of 1,024
     positions, half of every head rotated with stretched frequencies; a token input of 256
     features per layer."""
-    rot = {"base": 1e6, "dims": dim // 2, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    rot = {"base": 1e6, "dims": dim // 2, "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}}
 
     def layer(mlp, kv_from=None):
         m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
@@ -412,7 +412,7 @@ def fokurax_config(width, heads, kv_heads, dim, ff, vocab=32768):
     dense = {"kind": "dense", "ff": ff}
     experts = {"kind": "moe", "expert": {"ff": ff // 2}, "router": {"experts": 8, "top": 2}}
     return {"architecture": "Fokurax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
-            "embedding": {"scale": 1.0}, "residual_mult": 0.5, "logit_softcap": 30.0, "token_side": {"dim": 256},
+            "embedding": {"scale": 1.0}, "residual_mult": 0.7, "logit_softcap": 30.0, "token_side": {"dim": 256},
             "layers": [layer(dense), layer(experts), layer(experts, 1), layer(experts, 1), layer(dense),
                        layer(experts, 4)]}
 

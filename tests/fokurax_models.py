@@ -7,7 +7,7 @@ whole head and over a part of it, with and without stretched frequencies and
 without any rotation, blocks of 5 to 128 positions and no blocks at all, layers
 that read the cache of a layer right before them or further back, layers
 without a feed-forward, dense ones, experts with one, two and three choices out
-of 3 to 12, with and without the token input, the logit cap and the scales.
+of 3 to 10, with and without the token input, the logit cap and the scales.
 The token input has 11 features or more in these models: with 3 to 8 of them the direction
 of y = P g hangs on so few rounded numbers that, after y is divided by its root mean square,
 single positions of a bfloat16 run are 3 to 19 % of the largest logit away from the 32-bit
@@ -26,7 +26,7 @@ from typing import Dict, List, Optional
 import torch
 
 
-def rot(dims, base=10000.0, factor=None, original=64, fast=32.0, slow=1.0):
+def rot(dims, base=10000.0, factor=None, original=64, fast=12.0, slow=1.5):
     r = {"base": base, "dims": dims}
     if factor is not None:
         r["scaling"] = {"factor": factor, "original": original, "fast": fast, "slow": slow}
@@ -70,11 +70,11 @@ CONFIGS: Dict[str, dict] = {
                       layer(2, 2, 16, mlp=dense(80))]},
     # sizes that the tensor-core kernels take (head sizes 64 and 128, equal value size), blocks of 128 and of 50,
     # a reader right after its source and one two layers on, layers of different shapes
-    "F3": {"architecture": "Fokurax", "vocab": 512, "width": 256, "norm": {"eps": 1e-5}, "embedding": {"scale": 8.0},
-           "residual_mult": 0.5, "logit_softcap": 20.0, "token_side": {"dim": 16},
-           "layers": [layer(4, 2, 64, chunk=128, rotation=rot(32, 20000.0, factor=8.0, original=128, fast=16.0, slow=2.0),
-                            mlp=moe(128, 12, 2)),
-                      layer(4, 2, 64, chunk=128, rotation=rot(32, 20000.0, factor=8.0, original=128, fast=16.0, slow=2.0),
+    "F3": {"architecture": "Fokurax", "vocab": 512, "width": 256, "norm": {"eps": 2e-5}, "embedding": {"scale": 8.0},
+           "residual_mult": 0.6, "logit_softcap": 20.0, "token_side": {"dim": 16},
+           "layers": [layer(4, 2, 64, chunk=128, rotation=rot(32, 30000.0, factor=6.0, original=128, fast=16.0, slow=2.0),
+                            mlp=moe(128, 10, 2)),
+                      layer(4, 2, 64, chunk=128, rotation=rot(32, 30000.0, factor=6.0, original=128, fast=16.0, slow=2.0),
                             kv_from=0, mlp=dense(384)),
                       layer(2, 1, 128, chunk=50, rotation=rot(128, 1000.0), mlp=moe(64, 6, 1)),
                       layer(2, 1, 128, chunk=50, rotation=rot(128, 1000.0), kv_from=2, mlp=moe(64, 6, 3))]},

@@ -128,14 +128,14 @@ def test_attention_sees_its_block_and_nothing_before(kernels, dtype, d):
     page border), one right before the block's first position.  The first must take the
     weight, the second must not be seen, in a prompt and for a token decoded alone."""
     H = G = 2
-    T, page_size, chunk = 700, 16, 200
+    T, page_size, chunk = 700, 16, 180
     g = torch.Generator().manual_seed(3)
     q = torch.randn(T, H, d, generator=g) * 0.3
     k = torch.randn(T, G, d, generator=g) * 0.3
     v = torch.randn(T, G, d, generator=g)
     direction = torch.randn(d, generator=g)
     direction /= direction.norm()
-    inside, outside = 3 * chunk + 15, 3 * chunk - 1             # positions 615 and 599; queries at 699 and 660
+    inside, outside = 3 * chunk + 19, 3 * chunk - 1             # positions 559 (a page's last) and 539; queries at 699 and 660
     k[inside] = 8 * direction
     k[outside] = 8 * direction
     k[3 * chunk] = 8 * direction                                  # the block's first position
