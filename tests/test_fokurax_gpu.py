@@ -216,7 +216,7 @@ def test_gated_activation_with_biases(kernels, dtype, kind):
 @pytest.mark.parametrize("T,D,F,E,top", [(1, 64, 40, 5, 2), (9, 96, 24, 3, 3), (300, 80, 100, 7, 1), (700, 128, 64, 4, 2),
                                          (33, 72, 130, 12, 5), (3, 96, 32, 6, 2), (1000, 160, 96, 5, 3),
                                          (130, 256, 224, 3, 1), (70, 192, 128, 4, 2), (5, 256, 320, 9, 3),
-                                         (300, 192, 128, 5, 3), (2048, 256, 192, 8, 2)])
+                                         (300, 192, 128, 5, 3), (2048, 256, 192, 8, 2), (1, 128, 64, 4, 2)])
 def test_experts_chosen_by_a_table(kernels, dtype, T, D, F, E, top):
     """Few tokens (every tile holds a row or two), many (several tiles an expert), sizes
     that end inside a tile, tokens that repeat, experts that nobody uses.  With sizes that
